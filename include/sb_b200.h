@@ -1,0 +1,140 @@
+/*
+ * sb_b200.h -- C ABI of the B200 (sm_100a) stick-breaking attention kernels.
+ *
+ * Plain C: device pointers, sizes and element strides only; no framework types.  The caller owns
+ * every buffer (inputs, outputs, saved state, workspace, status word); the library keeps nothing
+ * between calls except per-process caches of driver entry points and kernel attributes.  Every
+ * entry point only enqueues work on the given stream and never synchronises.  Calls on different
+ * streams or devices may run concurrently as long as they do not share output or workspace memory.
+ *
+ * Tensor convention (same as the reference operators): q, k, v, o and their gradients are
+ * (batch, heads, tokens, head_dim) with arbitrary element strides for the first three axes and a
+ * unit stride on head_dim.  A packed variable-length batch is batch == 1 with `cu_seqlens` holding
+ * the END offset of every sequence (no leading zero), exactly what
+ * stickbreaking_attention/sb_varlen/__init__.py:71-78 hands to its kernels after stripping the zero.
+ * A fixed-length batch passes cu_seqlens == NULL.
+ */
+#ifndef SB_B200_H_
+#define SB_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SB_EXPORT __attribute__((visibility("default")))
+#else
+#define SB_EXPORT
+#endif
+
+enum SbDtype { SB_DTYPE_F32 = 0, SB_DTYPE_BF16 = 1, SB_DTYPE_F16 = 2 };
+
+enum SbStatus {
+  SB_OK = 0,
+  SB_ERR_ARGUMENT = 1,     /* bad shape, stride, pointer or struct size; see sb_last_error()  */
+  SB_ERR_WORKSPACE = 2,    /* workspace missing or smaller than sb_workspace_bytes()          */
+  SB_ERR_CUDA = 3,         /* a CUDA runtime/driver call failed; see sb_last_error()          */
+  SB_ERR_NO_DEVICE_CODE = 4 /* device is not sm_100: there is no other code path              */
+};
+
+/* Codes the kernels write to status[0] (device memory, 4 x int32, caller-zeroed). */
+enum SbDeviceStatus {
+  SB_DEV_OK = 0,
+  SB_DEV_BAD_CU_SEQLENS = 1, /* not non-decreasing, beyond `tokens`, or longer than max_seqlen;
+                                status[1] = index of the offending sequence                    */
+  SB_DEV_WAIT_TIMEOUT = 2    /* a bounded on-chip wait gave up; status[1] = which barrier      */
+};
+
+enum SbKernelPath {
+  SB_PATH_SIMT = 0,     /* fp32 arithmetic on CUDA cores: fp32 tensors and irregular head_dim  */
+  SB_PATH_TCGEN05 = 1   /* tcgen05 MMAs with TMEM accumulators, TMA-staged tiles: bf16 / fp16  */
+};
+
+enum SbFlags {
+  SB_FLAG_FORCE_SIMT = 1, /* run the CUDA-core kernels even where the tensor-core ones apply   */
+  SB_FLAG_CHECK_LEADING_ZERO = 2, /* cu_seqlens points one past the caller's leading 0 (the
+                            `zero_start` form of sb_varlen/__init__.py:72-74): the element before
+                            cu_seqlens[0] is read and must be 0, else SB_DEV_BAD_CU_SEQLENS with
+                            status[1] = -1.  Replaces the reference's host-side assert, which
+                            forces a device synchronisation.                                    */
+  SB_FLAG_BWD_SKIP_DKV = 4, /* timing aid: sb_bwd enqueues only the dQ kernel                   */
+  SB_FLAG_BWD_SKIP_DQ = 8   /* timing aid: sb_bwd enqueues only the dK/dV kernel, which then reads
+                            the boundary values a previous full sb_bwd left in the same workspace */
+};
+
+typedef struct SbTensor {
+  void *ptr;        /* device pointer to element (0,0,0,0)                   */
+  int64_t stride_b; /* element strides; the head_dim stride is 1 by contract */
+  int64_t stride_h;
+  int64_t stride_t;
+} SbTensor;
+
+typedef struct SbParams {
+  int32_t struct_bytes; /* = sizeof(SbParams); checked                                          */
+  int32_t dtype;        /* SbDtype of q,k,v,o,rem and all gradients                             */
+  int32_t batch;        /* 1 for a packed variable-length batch                                 */
+  int32_t heads;
+  int32_t head_dim;     /* 1..256                                                               */
+  int32_t num_seq;      /* entries in cu_seqlens (0 when cu_seqlens == NULL)                    */
+  int64_t tokens;       /* size of the tokens axis                                              */
+  int32_t max_seqlen;   /* upper bound on any sequence length; 0 means `tokens`                 */
+  int32_t attend_current; /* 0: key j < query i (default of the reference); 1: j <= i           */
+  int32_t cu_seqlens_int64; /* element type of cu_seqlens: 0 = int32, 1 = int64                 */
+  float logit_scale;    /* multiplies <q,k>; the reference default is 1/sqrt(head_dim)          */
+  int32_t flags;        /* SbFlags                                                              */
+  int32_t reserved;
+  const void *cu_seqlens; /* device, num_seq sequence END offsets, or NULL                      */
+
+  SbTensor q, k, v;     /* in                                                                    */
+  SbTensor o;           /* out (forward)                                                         */
+  void *rem;            /* out (forward): (batch, heads, tokens) contiguous, `dtype`             */
+  double *log_rem;      /* forward out / backward in: (batch, heads, tokens) contiguous fp64,    *
+                         * sum over allowed keys of log2(1 - beta).  Plays the part of the       *
+                         * reference's fp32 `neg_log_acc` (sb_varlen_fwd.py:420,205).            */
+
+  SbTensor d_o;         /* in  (backward)                                                        */
+  const void *d_rem;    /* in  (backward): (batch, heads, tokens) contiguous, `dtype`            */
+  SbTensor dq, dk, dv;  /* out (backward); every covered row is written, none is accumulated     */
+
+  void *workspace;      /* device scratch of at least sb_workspace_bytes() bytes, 256-B aligned  */
+  size_t workspace_bytes;
+  int32_t *status;      /* device int32[4], zeroed by the caller, or NULL                        */
+} SbParams;
+
+/* Scratch bytes sb_fwd (backward == 0) or sb_bwd (backward != 0) needs for these shapes.  Looks at
+ * shapes, dtype, max_seqlen and flags only, never at device memory.  Stands in for the per-call
+ * allocations the reference makes inside its launchers (lock and count arrays,
+ * sb_varlen_bwd.py:568-573).  Returns (size_t)-1 for invalid parameters. */
+SB_EXPORT size_t sb_workspace_bytes(const SbParams *p, int backward);
+
+/* Forward: writes o, rem, log_rem for every token covered by a sequence (tokens past the last
+ * sequence end are zero-filled).  Replaces `_compileable_forward`, i.e. the custom ops
+ * stickbreaking_attention::varlen_fwd (sb_varlen_fwd.py:454-522) and ::attn_fwd
+ * (sb_attn/sb_fwd.py:177-253).  `stream` is a cudaStream_t.  Returns an SbStatus. */
+SB_EXPORT int sb_fwd(const SbParams *p, void *stream);
+
+/* Backward: reads q, k, v, log_rem, d_o, d_rem and writes dq, dk, dv.  Deterministic: no atomics,
+ * no locks, bitwise identical from run to run.  Replaces `_compileable_backward`, i.e. the custom
+ * ops ::varlen_bwd (sb_varlen_bwd.py:542-641) and ::attn_bwd (sb_attn/sb_bwd.py:208-297). */
+SB_EXPORT int sb_bwd(const SbParams *p, void *stream);
+
+/* Which kernels sb_fwd / sb_bwd run for these parameters (an SbKernelPath), or -1 if invalid. */
+SB_EXPORT int sb_kernel_path(const SbParams *p);
+
+/* Number of kernel launches the last sb_fwd / sb_bwd call of this thread enqueued. */
+SB_EXPORT int sb_last_launch_count(void);
+
+/* Text of the last error returned to this thread ("" if none). */
+SB_EXPORT const char *sb_last_error(void);
+
+SB_EXPORT int sb_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SB_B200_H_ */

@@ -1,0 +1,31 @@
+"""Stick-breaking attention for NVIDIA B200 (sm_100a): hand-written CUDA kernels behind the operator
+interface of shawntan/stickbreaking-attention.
+
+    from stickbreaking_attention_b200 import sb_attn, sb_attn_varlen
+
+``install_as_dropin()`` additionally makes ``import stickbreaking_attention`` (and its ``sb_varlen`` /
+``sb_attn`` submodules) resolve to this package, for code written against the reference.
+"""
+import sys as _sys
+
+from . import _cabi
+
+_cabi.load()   # fail at import time, loudly, if the CUDA library has not been built
+
+from . import ops, sb_attn as _sb_attn_mod, sb_varlen as _sb_varlen_mod  # noqa: E402
+from .ops import check_status, force_simt, kernel_launches, kernel_path  # noqa: E402
+from .sb_attn import sb_attn  # noqa: E402
+from .sb_varlen import sb_attn_varlen  # noqa: E402
+
+__all__ = ["sb_attn", "sb_attn_varlen", "check_status", "force_simt", "kernel_launches",
+           "kernel_path", "install_as_dropin", "ops"]
+
+
+def install_as_dropin(name: str = "stickbreaking_attention") -> None:
+    """Registers this package under the reference's import name (refuses to shadow an import that
+    already happened)."""
+    this = _sys.modules[__name__]
+    for alias, mod in ((name, this), (name + ".sb_varlen", _sb_varlen_mod), (name + ".sb_attn", _sb_attn_mod)):
+        if alias in _sys.modules and _sys.modules[alias] is not mod:
+            raise ImportError(f"{alias} is already imported from {_sys.modules[alias].__file__}")
+        _sys.modules[alias] = mod

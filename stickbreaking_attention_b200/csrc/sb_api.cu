@@ -1,0 +1,226 @@
+// C ABI of the library: argument checks, workspace layout, kernel selection, launches.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "sb_common.cuh"
+
+namespace sb {
+
+static thread_local char g_err[512] = "";
+static thread_local int g_launches = 0;
+
+static int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Workspace layout, a pure function of the shapes:
+//   [hdr 256 B][tile_prefix int32 x (num_seq+1)][pair_prefix int64 x (num_seq+1)]
+//   backward only: [R1 fp32 x chunk_heads x pairs_cap x tile][S2 same]
+struct Plan {
+  int path;
+  int tile;
+  int tiles_cap;
+  int n_max;
+  int max_seqlen;
+  long long pairs_cap;
+  size_t off_tile_prefix, off_pair_prefix, off_bnd;
+  size_t bnd_bytes_per_head;  // one of the two arrays
+  int chunk_heads;
+  size_t total_fwd, total_bwd;
+};
+
+constexpr size_t kBoundaryBudget = (size_t)8 << 30;  // scratch for R1 + S2 before heads are chunked
+
+static int check_tensor(const SbTensor &t, const char *name, bool required) {
+  if (t.ptr == nullptr) return required ? fail(SB_ERR_ARGUMENT, "%s.ptr is NULL", name) : SB_OK;
+  if (t.stride_t < 0 || t.stride_h < 0 || t.stride_b < 0) return fail(SB_ERR_ARGUMENT, "%s has a negative stride", name);
+  return SB_OK;
+}
+
+static bool tma_friendly(const SbTensor &t, int esize) {
+  if (reinterpret_cast<uintptr_t>(t.ptr) % 16) return false;
+  const long long m = 16 / esize;
+  return t.stride_t % m == 0 && t.stride_h % m == 0 && t.stride_b % m == 0 && t.stride_t > 0;
+}
+
+static int make_plan(const SbParams *p, Plan &pl) {
+  if (p == nullptr) return fail(SB_ERR_ARGUMENT, "params is NULL");
+  if (p->struct_bytes != (int)sizeof(SbParams))
+    return fail(SB_ERR_ARGUMENT, "struct_bytes %d != sizeof(SbParams) %d", p->struct_bytes, (int)sizeof(SbParams));
+  if (p->dtype < SB_DTYPE_F32 || p->dtype > SB_DTYPE_F16) return fail(SB_ERR_ARGUMENT, "unknown dtype %d", p->dtype);
+  if (p->batch < 1 || p->heads < 1 || p->heads > 65535) return fail(SB_ERR_ARGUMENT, "batch/heads out of range");
+  if (p->head_dim < 1 || p->head_dim > 256) return fail(SB_ERR_ARGUMENT, "head_dim %d outside 1..256", p->head_dim);
+  if (p->tokens < 0 || p->tokens > 0x7fffff00LL) return fail(SB_ERR_ARGUMENT, "tokens out of range");
+  if (p->cu_seqlens != nullptr) {
+    if (p->batch != 1) return fail(SB_ERR_ARGUMENT, "a packed batch (cu_seqlens given) needs batch == 1");
+    if (p->num_seq < 1) return fail(SB_ERR_ARGUMENT, "num_seq must be >= 1 with cu_seqlens");
+  } else if (p->num_seq != 0) {
+    return fail(SB_ERR_ARGUMENT, "num_seq must be 0 without cu_seqlens");
+  }
+  if (p->max_seqlen < 0) return fail(SB_ERR_ARGUMENT, "max_seqlen is negative");
+
+  const int esize = p->dtype == SB_DTYPE_F32 ? 4 : 2;
+  const bool tc = !(p->flags & SB_FLAG_FORCE_SIMT) && tc_supported(p->dtype, p->head_dim) &&
+                  tma_friendly(p->q, esize) && tma_friendly(p->k, esize) && tma_friendly(p->v, esize);
+  pl.path = tc ? SB_PATH_TCGEN05 : SB_PATH_SIMT;
+  pl.tile = tc ? kTcTile : kSimtTile;
+  const long long T = p->tokens;
+  pl.max_seqlen = (p->max_seqlen == 0 || p->max_seqlen > T) ? (int)T : p->max_seqlen;
+  if (p->cu_seqlens == nullptr) pl.max_seqlen = (int)T;
+  const long long n_all = (T + pl.tile - 1) / pl.tile;
+  pl.n_max = (int)((pl.max_seqlen + pl.tile - 1) / pl.tile);
+  if (p->cu_seqlens == nullptr) {
+    pl.tiles_cap = (int)(n_all * p->batch);
+    pl.pairs_cap = (long long)p->batch * (n_all * (n_all + 1) / 2);
+  } else {
+    pl.tiles_cap = (int)(n_all + p->num_seq);
+    pl.pairs_cap = ((long long)pl.tiles_cap * (pl.n_max + 1) + 1) / 2;
+  }
+  if (pl.tiles_cap < 1) pl.tiles_cap = 1;
+  pl.off_tile_prefix = 256;
+  pl.off_pair_prefix = align_up(pl.off_tile_prefix + sizeof(int) * (size_t)(p->num_seq + 1), 256);
+  pl.off_bnd = align_up(pl.off_pair_prefix + sizeof(long long) * (size_t)(p->num_seq + 1), 256);
+  pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * sizeof(float), 256);
+  size_t chunk = pl.bnd_bytes_per_head ? kBoundaryBudget / (2 * pl.bnd_bytes_per_head) : (size_t)p->heads;
+  if (chunk < 1) chunk = 1;
+  if (chunk > (size_t)p->heads) chunk = p->heads;
+  pl.chunk_heads = (int)chunk;
+  pl.total_fwd = pl.off_bnd;
+  pl.total_bwd = pl.off_bnd + 2 * pl.bnd_bytes_per_head * chunk;
+  return SB_OK;
+}
+
+static TensorRef ref_of(const SbTensor &t) {
+  return TensorRef{reinterpret_cast<char *>(t.ptr), (long long)t.stride_b, (long long)t.stride_h, (long long)t.stride_t};
+}
+
+static int device_ok() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(SB_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  static int cached_major[64];
+  if (dev < 0 || dev >= 64) return fail(SB_ERR_CUDA, "device ordinal %d not supported", dev);
+  if (cached_major[dev] == 0) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail(SB_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+    cached_major[dev] = major;
+  }
+  if (cached_major[dev] != 10)
+    return fail(SB_ERR_NO_DEVICE_CODE, "device %d has compute capability %d.x; this library holds sm_100a code only",
+                dev, cached_major[dev]);
+  return SB_OK;
+}
+
+static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParams &k) {
+  memset(&k, 0, sizeof(k));
+  int rc;
+  if ((rc = check_tensor(p->q, "q", true)) || (rc = check_tensor(p->k, "k", true)) || (rc = check_tensor(p->v, "v", true)))
+    return rc;
+  if (p->log_rem == nullptr) return fail(SB_ERR_ARGUMENT, "log_rem is NULL");
+  if (!backward) {
+    if ((rc = check_tensor(p->o, "o", true))) return rc;
+    if (p->rem == nullptr) return fail(SB_ERR_ARGUMENT, "rem is NULL");
+  } else {
+    if ((rc = check_tensor(p->d_o, "d_o", true)) || (rc = check_tensor(p->dq, "dq", true)) ||
+        (rc = check_tensor(p->dk, "dk", true)) || (rc = check_tensor(p->dv, "dv", true)))
+      return rc;
+    if (p->d_rem == nullptr) return fail(SB_ERR_ARGUMENT, "d_rem is NULL");
+  }
+  const size_t need = backward ? pl.total_bwd : pl.total_fwd;
+  if (p->workspace == nullptr || p->workspace_bytes < need)
+    return fail(SB_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", p->workspace_bytes, need);
+  if (reinterpret_cast<uintptr_t>(p->workspace) % 256) return fail(SB_ERR_WORKSPACE, "workspace is not 256-byte aligned");
+
+  k.q = ref_of(p->q); k.k = ref_of(p->k); k.v = ref_of(p->v); k.o = ref_of(p->o);
+  k.d_o = ref_of(p->d_o); k.dq = ref_of(p->dq); k.dk = ref_of(p->dk); k.dv = ref_of(p->dv);
+  k.rem = reinterpret_cast<char *>(p->rem);
+  k.d_rem = reinterpret_cast<const char *>(p->d_rem);
+  k.log_rem = p->log_rem;
+  k.cu = p->cu_seqlens;
+  k.cu64 = p->cu_seqlens_int64;
+  k.batch = p->batch; k.heads = p->heads; k.head_dim = p->head_dim; k.num_seq = p->num_seq;
+  k.tokens = p->tokens;
+  k.attend_current = p->attend_current ? 1 : 0;
+  k.scale = p->logit_scale;
+  k.check_leading_zero = (p->cu_seqlens != nullptr && (p->flags & SB_FLAG_CHECK_LEADING_ZERO)) ? 1 : 0;
+  k.skip_dq = (p->flags & SB_FLAG_BWD_SKIP_DQ) ? 1 : 0;
+  k.skip_dkv = (p->flags & SB_FLAG_BWD_SKIP_DKV) ? 1 : 0;
+  k.tile = pl.tile; k.tiles_cap = pl.tiles_cap; k.n_max = pl.n_max; k.max_seqlen = pl.max_seqlen;
+  char *ws = reinterpret_cast<char *>(p->workspace);
+  k.hdr = reinterpret_cast<int *>(ws);
+  k.tile_prefix = reinterpret_cast<int *>(ws + pl.off_tile_prefix);
+  k.pair_prefix = reinterpret_cast<long long *>(ws + pl.off_pair_prefix);
+  k.bnd_r1 = reinterpret_cast<float *>(ws + pl.off_bnd);
+  k.bnd_s2 = reinterpret_cast<float *>(ws + pl.off_bnd + pl.bnd_bytes_per_head * pl.chunk_heads);
+  k.pairs_cap = (long long)(pl.bnd_bytes_per_head / ((size_t)pl.tile * sizeof(float)));
+  k.status = p->status;
+  return SB_OK;
+}
+
+static int run(const SbParams *p, void *stream, bool backward) {
+  g_err[0] = 0;
+  g_launches = 0;
+  Plan pl;
+  int rc = make_plan(p, pl);
+  if (rc) return rc;
+  if ((rc = device_ok())) return rc;
+  KParams k;
+  if ((rc = fill_kparams(p, pl, backward, k))) return rc;
+  if (p->tokens == 0) return SB_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_prep(k, s);
+  g_launches += (p->cu_seqlens != nullptr) ? 2 : 1;
+  if (e != cudaSuccess) return fail(SB_ERR_CUDA, "prep launch: %s", cudaGetErrorString(e));
+  const int chunk = backward ? pl.chunk_heads : p->heads;
+  for (int h0 = 0; h0 < p->heads; h0 += chunk) {
+    k.head0 = h0;
+    k.head_cnt = (p->heads - h0 < chunk) ? p->heads - h0 : chunk;
+    if (pl.path == SB_PATH_TCGEN05)
+      e = backward ? launch_tc_bwd(k, p->dtype, s, &g_launches) : launch_tc_fwd(k, p->dtype, s, &g_launches);
+    else
+      e = backward ? launch_simt_bwd(k, p->dtype, s, &g_launches) : launch_simt_fwd(k, p->dtype, s, &g_launches);
+    if (e != cudaSuccess) return fail(SB_ERR_CUDA, "%s launch: %s", backward ? "backward" : "forward", cudaGetErrorString(e));
+    if (p->cu_seqlens != nullptr) {
+      e = launch_zero_tail(k, p->dtype, backward, s);
+      g_launches += 1;
+      if (e != cudaSuccess) return fail(SB_ERR_CUDA, "tail launch: %s", cudaGetErrorString(e));
+    }
+  }
+  return SB_OK;
+}
+
+}  // namespace sb
+
+extern "C" {
+
+size_t sb_workspace_bytes(const SbParams *p, int backward) {
+  sb::Plan pl;
+  if (sb::make_plan(p, pl)) return (size_t)-1;
+  return backward ? pl.total_bwd : pl.total_fwd;
+}
+
+int sb_fwd(const SbParams *p, void *stream) { return sb::run(p, stream, false); }
+
+int sb_bwd(const SbParams *p, void *stream) { return sb::run(p, stream, true); }
+
+int sb_kernel_path(const SbParams *p) {
+  sb::Plan pl;
+  if (sb::make_plan(p, pl)) return -1;
+  return pl.path;
+}
+
+int sb_last_launch_count(void) { return sb::g_launches; }
+
+const char *sb_last_error(void) { return sb::g_err; }
+
+int sb_abi_version(void) { return SB_ABI_VERSION; }
+
+}  // extern "C"

@@ -1,0 +1,122 @@
+// Shared host/device definitions of the stick-breaking attention kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sb_b200.h"
+
+namespace sb {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr double kLog2eD = 1.4426950408889634074;
+constexpr double kLn2D = 0.69314718055994530942;
+
+struct TensorRef {
+  char *ptr;
+  long long sb, sh, st;  // element strides of batch, head, token
+};
+
+// Everything a kernel needs; passed by value.
+struct KParams {
+  TensorRef q, k, v, o, d_o, dq, dk, dv;
+  char *rem;
+  const char *d_rem;
+  double *log_rem;
+  const void *cu;      // sequence end offsets, or nullptr for a fixed-length batch
+  int cu64;
+  int batch, heads, head_dim, num_seq;
+  long long tokens;
+  int attend_current;
+  float scale;         // logit scale (natural units)
+  int head0, head_cnt; // heads [head0, head0 + head_cnt) are processed by this launch
+  int tile;            // rows per query tile == keys per key tile of the launch
+  int tiles_cap;       // upper bound on the number of query tiles over all sequences
+  int n_max;           // upper bound on tiles per sequence
+  int max_seqlen;
+  int check_leading_zero;  // the element before cu[0] must be 0
+  int skip_dq, skip_dkv;   // timing aids: leave one of the two backward kernels out
+  // workspace views
+  int *hdr;            // [0] abort flag, [1] end of the last sequence (varlen)
+  int *tile_prefix;    // [num_seq + 1]  exclusive prefix of tiles per sequence (varlen)
+  long long *pair_prefix;  // [num_seq + 1] exclusive prefix of n(n+1)/2 (varlen)
+  float *bnd_r1;       // [head_cnt][pairs_cap][tile]  suffix sums of log(1-beta) at tile starts
+  float *bnd_s2;       // [head_cnt][pairs_cap][tile]  prefix sums of G before each key tile
+  long long pairs_cap;
+  int *status;
+};
+
+// One (sequence, query-or-key tile) work item.
+struct TileCoord {
+  int seq;         // sequence (varlen) or batch element (fixed)
+  int idx;         // tile index inside the sequence
+  int n_tiles;     // tiles of this sequence
+  int len;         // sequence length
+  long long tok0;  // first token of the sequence on the tokens axis
+  long long boff;  // batch element (fixed) else 0
+  long long pair0; // first (query tile, key tile) pair slot of this sequence
+};
+
+__device__ __forceinline__ long long load_cu(const KParams &p, int i) {
+  return p.cu64 ? reinterpret_cast<const long long *>(p.cu)[i]
+                : (long long)reinterpret_cast<const int *>(p.cu)[i];
+}
+
+// Maps a flat work-item number to its sequence and tile.  Heavier (later) query tiles come first
+// inside a sequence when `reverse` is set, so that the longest-running blocks start earliest.
+__device__ __forceinline__ bool decode_tile(const KParams &p, int item, bool reverse, TileCoord &c) {
+  if (p.cu == nullptr) {
+    const int n = (int)((p.tokens + p.tile - 1) / p.tile);
+    if (item >= n * p.batch) return false;
+    c.seq = item / n;
+    c.idx = item - c.seq * n;
+    c.n_tiles = n;
+    c.len = (int)p.tokens;
+    c.tok0 = 0;
+    c.boff = c.seq;
+    c.pair0 = (long long)c.seq * ((long long)n * (n + 1) / 2);
+  } else {
+    const int total = p.tile_prefix[p.num_seq];
+    if (item >= total) return false;
+    int lo = 0, hi = p.num_seq - 1;  // last sequence whose prefix <= item
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.tile_prefix[mid] <= item) lo = mid; else hi = mid - 1;
+    }
+    c.seq = lo;
+    c.idx = item - p.tile_prefix[lo];
+    c.n_tiles = p.tile_prefix[lo + 1] - p.tile_prefix[lo];
+    c.tok0 = lo == 0 ? 0 : load_cu(p, lo - 1);
+    c.len = (int)(load_cu(p, lo) - c.tok0);
+    c.boff = 0;
+    c.pair0 = p.pair_prefix[lo];
+  }
+  if (reverse) c.idx = c.n_tiles - 1 - c.idx;
+  return true;
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+// Host-side launch helpers implemented in the .cu files; all return cudaError_t of the launch.
+cudaError_t launch_prep(const KParams &p, cudaStream_t s);
+cudaError_t launch_zero_tail(const KParams &p, int dtype, bool backward, cudaStream_t s);
+cudaError_t launch_simt_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
+cudaError_t launch_simt_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
+cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
+cudaError_t launch_tc_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
+bool tc_supported(int dtype, int head_dim);
+
+constexpr int kSimtTile = 32;
+constexpr int kTcTile = 128;
+
+}  // namespace sb

@@ -1,0 +1,424 @@
+// CUDA-core (fp32 FMA) kernels: the exact path for fp32 tensors and for head sizes the tensor-core
+// kernels do not take.  Also holds the two helper kernels every path uses: the sequence-table
+// builder and the tail zero-fill.
+//
+// Structure (shared with the tensor-core path):
+//   forward      one block per (sequence, 32-row query tile, head); key tiles are walked from the
+//                diagonal back to the sequence start while every row carries sum softplus(z), so the
+//                log-space suffix sum needs no second pass              (reference: _forward_one_row,
+//                sb_varlen_fwd.py:81-215)
+//   backward A   query-stationary, key tiles 0 -> diagonal: dQ, plus the per-(row, key tile)
+//                boundary values R1 (suffix sum of log(1-beta) from this key tile on) and S2 (prefix sum
+//                of G before this key tile)                             (reference: _backward_one_row,
+//                sb_varlen_bwd.py:297-481, which adds dK/dV under a spin lock instead)
+//   backward B   key-stationary: recomputes each tile from R1/S2 and accumulates dK, dV in registers;
+//                no atomics, no locks, fixed summation order.
+#include "sb_common.cuh"
+
+namespace sb {
+
+// ------------------------------------------------------------------------------------------------
+// Sequence table: exclusive prefix of tiles per sequence and of (query tile, key tile) pairs.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prep_kernel(KParams p) {
+  __shared__ long long s_tiles[256];
+  __shared__ long long s_pairs[256];
+  const int t = threadIdx.x;
+  const int per = (p.num_seq + 255) / 256;
+  const int s0 = t * per, s1 = min(p.num_seq, s0 + per);
+  long long tiles = 0, pairs = 0;
+  int bad = -1;
+  for (int s = s0; s < s1; ++s) {
+    const long long start = s == 0 ? 0 : load_cu(p, s - 1);
+    const long long end = load_cu(p, s);
+    const long long len = end - start;
+    if (len < 0 || end > p.tokens || start < 0 || len > p.max_seqlen) { if (bad < 0) bad = s; continue; }
+    const long long n = (len + p.tile - 1) / p.tile;
+    tiles += n;
+    pairs += n * (n + 1) / 2;
+  }
+  s_tiles[t] = tiles;
+  s_pairs[t] = pairs;
+  if (bad >= 0) {
+    p.hdr[0] = 1;
+    if (p.status != nullptr) { p.status[0] = SB_DEV_BAD_CU_SEQLENS; p.status[1] = bad; }
+  }
+  __syncthreads();
+  if (t == 0) {
+    if (p.check_leading_zero && load_cu(p, -1) != 0) {
+      p.hdr[0] = 1;
+      if (p.status != nullptr) { p.status[0] = SB_DEV_BAD_CU_SEQLENS; p.status[1] = -1; }
+    }
+    long long a = 0, b = 0;
+    for (int i = 0; i < 256; ++i) {
+      const long long x = s_tiles[i], y = s_pairs[i];
+      s_tiles[i] = a; s_pairs[i] = b;
+      a += x; b += y;
+    }
+    p.tile_prefix[p.num_seq] = (int)a;
+    p.pair_prefix[p.num_seq] = b;
+    p.hdr[1] = p.num_seq > 0 ? (int)load_cu(p, p.num_seq - 1) : 0;
+    if (a > p.tiles_cap || b > p.pairs_cap) p.hdr[0] = 1;  // cannot happen for valid cu_seqlens
+  }
+  __syncthreads();
+  tiles = s_tiles[t];
+  pairs = s_pairs[t];
+  for (int s = s0; s < s1; ++s) {
+    p.tile_prefix[s] = (int)tiles;
+    p.pair_prefix[s] = pairs;
+    const long long start = s == 0 ? 0 : load_cu(p, s - 1);
+    const long long len = load_cu(p, s) - start;
+    if (len < 0 || len > p.max_seqlen) continue;
+    const long long n = (len + p.tile - 1) / p.tile;
+    tiles += n;
+    pairs += n * (n + 1) / 2;
+  }
+}
+
+__global__ void clear_hdr_kernel(int *hdr) { if (threadIdx.x < 4) hdr[threadIdx.x] = 0; }
+
+cudaError_t launch_prep(const KParams &p, cudaStream_t s) {
+  clear_hdr_kernel<<<1, 32, 0, s>>>(p.hdr);
+  if (p.cu != nullptr) prep_kernel<<<1, 256, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+// Rows past the end of the last packed sequence belong to no sequence: write zeros there.
+template <typename T>
+__global__ void zero_tail_kernel(KParams p, bool backward) {
+  if (p.hdr[0]) return;
+  const long long first = p.hdr[1];
+  const int h = p.head0 + blockIdx.y;
+  const int d = p.head_dim;
+  for (long long row = first + blockIdx.x; row < p.tokens; row += gridDim.x) {
+    if (!backward) {
+      T *o = reinterpret_cast<T *>(p.o.ptr) + h * p.o.sh + row * p.o.st;
+      for (int x = threadIdx.x; x < d; x += blockDim.x) o[x] = from_f32<T>(0.f);
+      if (threadIdx.x == 0) {
+        reinterpret_cast<T *>(p.rem)[(long long)h * p.tokens + row] = from_f32<T>(0.f);
+        p.log_rem[(long long)h * p.tokens + row] = 0.0;
+      }
+    } else {
+      T *a = reinterpret_cast<T *>(p.dq.ptr) + h * p.dq.sh + row * p.dq.st;
+      T *b = reinterpret_cast<T *>(p.dk.ptr) + h * p.dk.sh + row * p.dk.st;
+      T *c = reinterpret_cast<T *>(p.dv.ptr) + h * p.dv.sh + row * p.dv.st;
+      for (int x = threadIdx.x; x < d; x += blockDim.x) { a[x] = b[x] = c[x] = from_f32<T>(0.f); }
+    }
+  }
+}
+
+cudaError_t launch_zero_tail(const KParams &p, int dtype, bool backward, cudaStream_t s) {
+  if (p.cu == nullptr) return cudaSuccess;
+  dim3 grid(8, p.head_cnt);
+  if (dtype == SB_DTYPE_F32) zero_tail_kernel<float><<<grid, 128, 0, s>>>(p, backward);
+  else if (dtype == SB_DTYPE_BF16) zero_tail_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p, backward);
+  else zero_tail_kernel<__half><<<grid, 128, 0, s>>>(p, backward);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// SIMT kernels.  256 threads; thread t owns output row t/8 and columns (t%8) + 8u.
+// ------------------------------------------------------------------------------------------------
+constexpr int kT = kSimtTile;   // 32
+constexpr int kLdS = kT + 1;
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+template <typename T>
+__device__ __forceinline__ void load_rows(float *dst, int ld, const TensorRef &t, const TileCoord &c, int h,
+                                          int tile_idx, int d) {
+  const T *base = reinterpret_cast<const T *>(t.ptr) + c.boff * t.sb + (long long)h * t.sh;
+  for (int e = threadIdx.x; e < kT * d; e += blockDim.x) {
+    const int r = e / d, x = e - r * d;
+    const int li = tile_idx * kT + r;
+    dst[r * ld + x] = li < c.len ? to_f32<T>(base[(c.tok0 + li) * t.st + x]) : 0.f;
+  }
+}
+
+// S[r][c] = scale * <A_r, B_c> for the 4 columns of this thread.
+__device__ __forceinline__ void tile_dot(float *S, const float *A, const float *B, int ld, int d, float scale) {
+  const int r = threadIdx.x >> 3, cg = threadIdx.x & 7;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  const float *a = A + r * ld;
+  const float *b0 = B + cg * ld, *b1 = b0 + 8 * ld, *b2 = b0 + 16 * ld, *b3 = b0 + 24 * ld;
+  for (int x = 0; x < d; ++x) {
+    const float av = a[x];
+    s0 = fmaf(av, b0[x], s0); s1 = fmaf(av, b1[x], s1); s2 = fmaf(av, b2[x], s2); s3 = fmaf(av, b3[x], s3);
+  }
+  S[r * kLdS + cg] = s0 * scale; S[r * kLdS + cg + 8] = s1 * scale;
+  S[r * kLdS + cg + 16] = s2 * scale; S[r * kLdS + cg + 24] = s3 * scale;
+}
+
+template <typename T, int U>
+__global__ void __launch_bounds__(256) simt_fwd_kernel(KParams p) {
+  extern __shared__ float smem[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x, true, c)) return;
+  const int d = p.head_dim, ld = d + 1;
+  float *Qs = smem, *Ks = Qs + kT * ld, *Vs = Ks + kT * ld, *Ss = Vs + kT * ld;
+  const int h = p.head0 + blockIdx.y;
+  const int t = threadIdx.x, r = t >> 3, cg = t & 7;
+  const int I = c.idx;
+
+  load_rows<T>(Qs, ld, p.q, c, h, I, d);
+  float acc[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) acc[u] = 0.f;
+  float run_sp = 0.f;  // sum of softplus(z) over the key tiles already visited (rows of warp 0)
+
+  for (int J = I; J >= 0; --J) {
+    load_rows<T>(Ks, ld, p.k, c, h, J, d);
+    load_rows<T>(Vs, ld, p.v, c, h, J, d);
+    __syncthreads();
+    tile_dot(Ss, Qs, Ks, ld, d, p.scale);
+    __syncthreads();
+    if (t < kT) {
+      const int gi = I * kT + t;
+      float suffix = 0.f;
+      for (int j = kT - 1; j >= 0; --j) {
+        const int gj = J * kT + j;
+        const bool allowed = gi < c.len && (p.attend_current ? gj <= gi : gj < gi);
+        const float z = Ss[t * kLdS + j];
+        float a = 0.f;
+        if (allowed) {
+          suffix += softplus_f(z);
+          a = expf(z - run_sp - suffix);
+        }
+        Ss[t * kLdS + j] = a;
+      }
+      run_sp += suffix;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int x = cg + 8 * u;
+      if (x < d) {
+        float s = acc[u];
+        for (int j = 0; j < kT; ++j) s = fmaf(Ss[r * kLdS + j], Vs[j * ld + x], s);
+        acc[u] = s;
+      }
+    }
+    __syncthreads();
+  }
+
+  const int gi = I * kT + r;
+  if (gi < c.len) {
+    T *o = reinterpret_cast<T *>(p.o.ptr) + c.boff * p.o.sb + (long long)h * p.o.sh + (c.tok0 + gi) * p.o.st;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int x = cg + 8 * u;
+      if (x < d) o[x] = from_f32<T>(acc[u]);
+    }
+  }
+  if (t < kT && I * kT + t < c.len) {
+    const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + I * kT + t;
+    reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(expf(-run_sp));
+    p.log_rem[idx] = -(double)run_sp * kLog2eD;
+  }
+}
+
+// Row pass of the backward: on entry Z holds z, P holds dP; on exit Z holds dz and P holds A.
+// r1 = sum of log(1-beta) over the allowed keys from this tile's first key on (<= 0).
+__device__ __forceinline__ void bwd_row_pass(float *Z, float *P, int row, int gi, int J, int len, int ac,
+                                             float r1, float gpre, float dr, float &sp_sum, float &g_sum) {
+  float spl = 0.f, gs = 0.f;
+  for (int j = 0; j < kT; ++j) {
+    const int gj = J * kT + j;
+    const bool allowed = gi < len && (ac ? gj <= gi : gj < gi);
+    const float z = Z[row * kLdS + j];
+    float a = 0.f, dz = 0.f;
+    if (allowed) {
+      a = expf(z + r1 + spl);
+      spl += softplus_f(z);
+      const float g = a * (P[row * kLdS + j] - dr);
+      gs += g;
+      const float beta = 1.f / (1.f + expf(-z));
+      dz = g - beta * (gpre + gs);
+    }
+    Z[row * kLdS + j] = dz;
+    P[row * kLdS + j] = a;
+  }
+  sp_sum = spl;
+  g_sum = gs;
+}
+
+template <typename T, int U>
+__global__ void __launch_bounds__(256) simt_bwd_dq_kernel(KParams p) {
+  extern __shared__ float smem[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x, true, c)) return;
+  const int d = p.head_dim, ld = d + 1;
+  float *Qs = smem, *Gs = Qs + kT * ld, *Ks = Gs + kT * ld, *Vs = Ks + kT * ld;
+  float *Zs = Vs + kT * ld, *Ps = Zs + kT * kLdS;
+  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int t = threadIdx.x, r = t >> 3, cg = t & 7;
+  const int I = c.idx;
+
+  load_rows<T>(Qs, ld, p.q, c, h, I, d);
+  load_rows<T>(Gs, ld, p.d_o, c, h, I, d);
+  float acc[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) acc[u] = 0.f;
+  double r1 = 0.0;
+  float gpre = 0.f, dr = 0.f;
+  const int my_row = I * kT + t;
+  if (t < kT && my_row < c.len) {
+    const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + my_row;
+    r1 = p.log_rem[idx] * kLn2D;
+    dr = to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]);
+  }
+
+  for (int J = 0; J <= I; ++J) {
+    load_rows<T>(Ks, ld, p.k, c, h, J, d);
+    load_rows<T>(Vs, ld, p.v, c, h, J, d);
+    __syncthreads();
+    tile_dot(Zs, Qs, Ks, ld, d, p.scale);
+    tile_dot(Ps, Gs, Vs, ld, d, 1.f);
+    __syncthreads();
+    if (t < kT) {
+      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * kT + t;
+      p.bnd_r1[slot] = (float)r1;
+      p.bnd_s2[slot] = gpre;
+      float sp_sum, g_sum;
+      bwd_row_pass(Zs, Ps, t, my_row, J, c.len, p.attend_current, (float)r1, gpre, dr, sp_sum, g_sum);
+      r1 += (double)sp_sum;
+      gpre += g_sum;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int x = cg + 8 * u;
+      if (x < d) {
+        float s = acc[u];
+        for (int j = 0; j < kT; ++j) s = fmaf(Zs[r * kLdS + j], Ks[j * ld + x], s);
+        acc[u] = s;
+      }
+    }
+    __syncthreads();
+  }
+
+  const int gi = I * kT + r;
+  if (gi < c.len) {
+    T *o = reinterpret_cast<T *>(p.dq.ptr) + c.boff * p.dq.sb + (long long)h * p.dq.sh + (c.tok0 + gi) * p.dq.st;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int x = cg + 8 * u;
+      if (x < d) o[x] = from_f32<T>(acc[u] * p.scale);
+    }
+  }
+}
+
+template <typename T, int U>
+__global__ void __launch_bounds__(256) simt_bwd_dkv_kernel(KParams p) {
+  extern __shared__ float smem[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x, false, c)) return;
+  const int d = p.head_dim, ld = d + 1;
+  float *Qs = smem, *Gs = Qs + kT * ld, *Ks = Gs + kT * ld, *Vs = Ks + kT * ld;
+  float *Zs = Vs + kT * ld, *Ps = Zs + kT * kLdS;
+  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int t = threadIdx.x, r = t >> 3, cg = t & 7;
+  const int J = c.idx;
+
+  load_rows<T>(Ks, ld, p.k, c, h, J, d);
+  load_rows<T>(Vs, ld, p.v, c, h, J, d);
+  float dk[U], dv[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) { dk[u] = 0.f; dv[u] = 0.f; }
+
+  for (int I = J; I < c.n_tiles; ++I) {
+    load_rows<T>(Qs, ld, p.q, c, h, I, d);
+    load_rows<T>(Gs, ld, p.d_o, c, h, I, d);
+    __syncthreads();
+    tile_dot(Zs, Qs, Ks, ld, d, p.scale);
+    tile_dot(Ps, Gs, Vs, ld, d, 1.f);
+    __syncthreads();
+    if (t < kT) {
+      const int gi = I * kT + t;
+      float dr = 0.f;
+      if (gi < c.len)
+        dr = to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]);
+      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * kT + t;
+      float sp_sum, g_sum;
+      bwd_row_pass(Zs, Ps, t, gi, J, c.len, p.attend_current, p.bnd_r1[slot], p.bnd_s2[slot], dr, sp_sum, g_sum);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int x = cg + 8 * u;
+      if (x < d) {
+        float a = dk[u], b = dv[u];
+        for (int i = 0; i < kT; ++i) {
+          a = fmaf(Zs[i * kLdS + r], Qs[i * ld + x], a);
+          b = fmaf(Ps[i * kLdS + r], Gs[i * ld + x], b);
+        }
+        dk[u] = a; dv[u] = b;
+      }
+    }
+    __syncthreads();
+  }
+
+  const int gj = J * kT + r;
+  if (gj < c.len) {
+    T *ok = reinterpret_cast<T *>(p.dk.ptr) + c.boff * p.dk.sb + (long long)h * p.dk.sh + (c.tok0 + gj) * p.dk.st;
+    T *ov = reinterpret_cast<T *>(p.dv.ptr) + c.boff * p.dv.sb + (long long)h * p.dv.sh + (c.tok0 + gj) * p.dv.st;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int x = cg + 8 * u;
+      if (x < d) { ok[x] = from_f32<T>(dk[u] * p.scale); ov[x] = from_f32<T>(dv[u]); }
+    }
+  }
+}
+
+template <typename K>
+static cudaError_t launch_one(K kernel, const KParams &p, size_t smem, cudaStream_t s) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid(p.tiles_cap, p.head_cnt);
+  kernel<<<grid, 256, smem, s>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t simt_fwd_t(const KParams &p, cudaStream_t s) {
+  const size_t smem = (size_t)(3 * kT * (p.head_dim + 1) + kT * kLdS) * sizeof(float);
+  if (p.head_dim <= 64) return launch_one(simt_fwd_kernel<T, 8>, p, smem, s);
+  if (p.head_dim <= 128) return launch_one(simt_fwd_kernel<T, 16>, p, smem, s);
+  return launch_one(simt_fwd_kernel<T, 32>, p, smem, s);
+}
+
+template <typename T>
+static cudaError_t simt_bwd_t(const KParams &p, cudaStream_t s) {
+  const size_t smem = (size_t)(4 * kT * (p.head_dim + 1) + 2 * kT * kLdS) * sizeof(float);
+  cudaError_t e = cudaSuccess;
+  if (p.head_dim <= 64) {
+    if (!p.skip_dq) e = launch_one(simt_bwd_dq_kernel<T, 8>, p, smem, s);
+    if (e == cudaSuccess && !p.skip_dkv) e = launch_one(simt_bwd_dkv_kernel<T, 8>, p, smem, s);
+  } else if (p.head_dim <= 128) {
+    if (!p.skip_dq) e = launch_one(simt_bwd_dq_kernel<T, 16>, p, smem, s);
+    if (e == cudaSuccess && !p.skip_dkv) e = launch_one(simt_bwd_dkv_kernel<T, 16>, p, smem, s);
+  } else {
+    if (!p.skip_dq) e = launch_one(simt_bwd_dq_kernel<T, 32>, p, smem, s);
+    if (e == cudaSuccess && !p.skip_dkv) e = launch_one(simt_bwd_dkv_kernel<T, 32>, p, smem, s);
+  }
+  return e;
+}
+
+cudaError_t launch_simt_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches) {
+  *launches += 1;
+  if (dtype == SB_DTYPE_F32) return simt_fwd_t<float>(p, s);
+  if (dtype == SB_DTYPE_BF16) return simt_fwd_t<__nv_bfloat16>(p, s);
+  return simt_fwd_t<__half>(p, s);
+}
+
+cudaError_t launch_simt_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches) {
+  *launches += (p.skip_dq ? 0 : 1) + (p.skip_dkv ? 0 : 1);
+  if (dtype == SB_DTYPE_F32) return simt_bwd_t<float>(p, s);
+  if (dtype == SB_DTYPE_BF16) return simt_bwd_t<__nv_bfloat16>(p, s);
+  return simt_bwd_t<__half>(p, s);
+}
+
+}  // namespace sb

@@ -1,0 +1,265 @@
+"""Host launchers and ``torch.library`` operators over the C ABI.
+
+Mirrors the reference's launcher layer: ``varlen_fwd`` / ``varlen_bwd``
+(``sb_varlen/sb_varlen_fwd.py:413-522``, ``sb_varlen/sb_varlen_bwd.py:484-641``) and the fixed-length
+``attn_fwd`` / ``attn_bwd`` (``sb_attn/sb_fwd.py:139-253``, ``sb_attn/sb_bwd.py:163-297``).  Like the
+reference (``utils.py:12-39``) each launcher is also registered as a mutating custom operator and is
+routed through it only while ``torch.compile`` is tracing.  The operator namespace is
+``stickbreaking_attention_b200`` so that both packages can be imported in one process.
+
+Differences from the reference launchers, all on purpose:
+
+* the saved state is ``log_rem`` (fp64, base-2) instead of the fp32 ``neg_log_acc``;
+* ``max_seqlens`` is only an upper bound used to size scratch memory and may be ``None``;
+* nothing is zero-initialised with separate memsets: the kernels write every output row;
+* ``cu_seqlens`` is validated on the device into a status word (``check_status``), so no launcher
+  synchronises with the host.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Optional
+
+import torch
+
+from . import _cabi
+
+NAMESPACE = "stickbreaking_attention_b200"
+
+_state = {"force_simt": False, "launches": 0}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+@contextlib.contextmanager
+def force_simt(enabled: bool = True):
+    """Within the block, bf16/fp16 calls run the CUDA-core kernels too (a cross-check in tests)."""
+    old = _state["force_simt"]
+    _state["force_simt"] = enabled
+    try:
+        yield
+    finally:
+        _state["force_simt"] = old
+
+
+def kernel_launches() -> int:
+    """Total kernel launches enqueued by this module since import (for benchmark accounting)."""
+    return _state["launches"]
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        word = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_words[idx] = word
+    return word
+
+
+def check_status(device=None) -> None:
+    """Reads (synchronising) the device status word written by the kernels, clears it, and raises
+    ``SbError`` if a kernel reported a problem since the last check."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(device)
+    vals = word.tolist()
+    if vals[0] != 0:
+        word.zero_()
+        msg = _cabi.SB_DEV_MESSAGES.get(vals[0], "unknown device status {0}").format(vals[1])
+        raise _cabi.SbError(f"device status {vals[0]}: {msg}")
+
+
+def _require(cond: bool, msg: str):
+    if not cond:
+        raise ValueError(msg)
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """Unit innermost stride, 16-byte aligned base and outer strides; copies only if needed."""
+    mult = 16 // t.element_size()
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(
+        s % mult == 0 or n == 1 for s, n in zip(t.stride()[:-1], t.shape[:-1]))
+    if t.shape[-1] % mult != 0:          # rows cannot be 16-byte multiples anyway
+        ok = t.stride(-1) == 1
+    return t if ok else t.contiguous()
+
+
+def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero):
+    _require(q.is_cuda, "stick-breaking attention runs on a CUDA device only (no CPU path)")
+    _require(q.dtype in _cabi.SB_DTYPE, f"unsupported dtype {q.dtype}")
+    _require(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype")
+    _require(q.shape == k.shape == v.shape, "q, k, v must share a shape")
+    _require(q.dim() == (4 if fixed else 3), "expected (B,H,T,d) for sb_attn and (H,T,d) for sb_attn_varlen")
+    prm.struct_bytes = _cabi.ctypes.sizeof(_cabi.SbParams)
+    prm.dtype = _cabi.SB_DTYPE[q.dtype]
+    if fixed:
+        prm.batch, prm.heads, prm.tokens, prm.head_dim = q.shape
+        prm.num_seq = 0
+        prm.cu_seqlens = None
+    else:
+        prm.batch = 1
+        prm.heads, prm.tokens, prm.head_dim = q.shape
+        _require(cu_seqlens.is_cuda and cu_seqlens.dim() == 1, "cu_seqlens must be a 1-D CUDA tensor")
+        _require(cu_seqlens.dtype in (torch.int32, torch.int64), "cu_seqlens must be int32 or int64")
+        _require(cu_seqlens.stride(0) == 1, "cu_seqlens must be contiguous")
+        prm.num_seq = cu_seqlens.numel()
+        prm.cu_seqlens = cu_seqlens.data_ptr()
+        prm.cu_seqlens_int64 = int(cu_seqlens.dtype == torch.int64)
+    prm.max_seqlen = 0 if max_seqlens is None else int(max_seqlens)
+    prm.attend_current = int(bool(attend_current))
+    prm.logit_scale = float(logit_scale)
+    prm.flags = (_cabi.SB_FLAG_FORCE_SIMT if _state["force_simt"] else 0) | \
+                (_cabi.SB_FLAG_CHECK_LEADING_ZERO if leading_zero else 0)
+    prm.q = _cabi.tensor_arg(q, fixed)
+    prm.k = _cabi.tensor_arg(k, fixed)
+    prm.v = _cabi.tensor_arg(v, fixed)
+
+
+def _run(backward: bool, prm, device):
+    lib = _cabi.load()
+    need = lib.sb_workspace_bytes(prm, int(backward))
+    if need == 2 ** 64 - 1:
+        raise _cabi.SbError(f"invalid parameters: {lib.sb_last_error().decode()}")
+    workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+    prm.workspace = workspace.data_ptr()
+    prm.workspace_bytes = workspace.numel()
+    prm.status = _status_word(device).data_ptr()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    with torch.cuda.device(device):
+        rc = (lib.sb_bwd if backward else lib.sb_fwd)(prm, stream)
+    _cabi.check_call(lib, rc, "sb_bwd" if backward else "sb_fwd")
+    _state["launches"] += lib.sb_last_launch_count()
+    # the caching allocator keeps `workspace` alive until the stream has passed this point
+    return workspace
+
+
+def _fwd_impl(fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero,
+              o, rem, log_rem):
+    prm = _cabi.SbParams()
+    _fill(prm, fixed=fixed, q=q, k=k, v=v, cu_seqlens=cu_seqlens, max_seqlens=max_seqlens,
+          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero)
+    prm.o = _cabi.tensor_arg(o, fixed)
+    prm.rem = rem.data_ptr()
+    prm.log_rem = log_rem.data_ptr()
+    _run(False, prm, q.device)
+
+
+def _bwd_impl(fixed, do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current,
+              leading_zero, dq, dk, dv):
+    prm = _cabi.SbParams()
+    _fill(prm, fixed=fixed, q=q, k=k, v=v, cu_seqlens=cu_seqlens, max_seqlens=max_seqlens,
+          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero)
+    prm.log_rem = log_rem.data_ptr()
+    prm.d_o = _cabi.tensor_arg(do, fixed)
+    prm.d_rem = dr.data_ptr()
+    prm.dq = _cabi.tensor_arg(dq, fixed)
+    prm.dk = _cabi.tensor_arg(dk, fixed)
+    prm.dv = _cabi.tensor_arg(dv, fixed)
+    _run(True, prm, q.device)
+
+
+# ---- custom operators (same four names as the reference registers) ---------------------------------
+
+@torch.library.custom_op(f"{NAMESPACE}::varlen_fwd", mutates_args={"o", "rem", "log_rem"}, device_types="cuda")
+def _op_varlen_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                   max_seqlens: int, logit_scale: float, attend_current: bool, leading_zero: bool,
+                   o: torch.Tensor, rem: torch.Tensor, log_rem: torch.Tensor) -> None:
+    _fwd_impl(False, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero, o, rem, log_rem)
+
+
+@torch.library.custom_op(f"{NAMESPACE}::varlen_bwd", mutates_args={"dq", "dk", "dv"}, device_types="cuda")
+def _op_varlen_bwd(do: torch.Tensor, dr: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                   cu_seqlens: torch.Tensor, max_seqlens: int, log_rem: torch.Tensor, logit_scale: float,
+                   attend_current: bool, leading_zero: bool, dq: torch.Tensor, dk: torch.Tensor,
+                   dv: torch.Tensor) -> None:
+    _bwd_impl(False, do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current,
+              leading_zero, dq, dk, dv)
+
+
+@torch.library.custom_op(f"{NAMESPACE}::attn_fwd", mutates_args={"o", "rem", "log_rem"}, device_types="cuda")
+def _op_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, logit_scale: float, attend_current: bool,
+                 o: torch.Tensor, rem: torch.Tensor, log_rem: torch.Tensor) -> None:
+    _fwd_impl(True, q, k, v, None, None, logit_scale, attend_current, False, o, rem, log_rem)
+
+
+@torch.library.custom_op(f"{NAMESPACE}::attn_bwd", mutates_args={"dq", "dk", "dv"}, device_types="cuda")
+def _op_attn_bwd(do: torch.Tensor, dr: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                 log_rem: torch.Tensor, logit_scale: float, attend_current: bool, dq: torch.Tensor,
+                 dk: torch.Tensor, dv: torch.Tensor) -> None:
+    _bwd_impl(True, do, dr, q, k, v, None, None, log_rem, logit_scale, attend_current, False, dq, dk, dv)
+
+
+def _compiling() -> bool:
+    return torch.compiler.is_compiling()
+
+
+# ---- launchers -----------------------------------------------------------------------------------
+
+def _strip(cu_seqlens, leading_zero):
+    return cu_seqlens[1:] if leading_zero else cu_seqlens
+
+
+def varlen_fwd(q, k, v, cu_seqlens, max_seqlens: Optional[int], logit_scale: float,
+               attend_current: bool = False, leading_zero: bool = False):
+    """Packed forward.  ``cu_seqlens`` holds sequence ends, preceded by a 0 iff ``leading_zero``.
+    Returns ``(o, rem, log_rem)`` like the reference returns ``(o, rem, neg_log_acc)``."""
+    q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+    o = torch.empty_like(q)
+    rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
+    log_rem = torch.empty(q.shape[:-1], dtype=torch.float64, device=q.device)
+    ends = _strip(cu_seqlens, leading_zero)
+    if _compiling():
+        _op_varlen_fwd(q, k, v, ends, 0 if max_seqlens is None else int(max_seqlens), float(logit_scale),
+                       bool(attend_current), bool(leading_zero), o, rem, log_rem)
+    else:
+        _fwd_impl(False, q, k, v, ends, max_seqlens, logit_scale, attend_current, leading_zero, o, rem, log_rem)
+    return o, rem, log_rem
+
+
+def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens: Optional[int], log_rem, logit_scale: float,
+               attend_current: bool = False, leading_zero: bool = False):
+    """Packed backward; returns ``(dq, dk, dv)`` in the dtype of the inputs."""
+    q, k, v, do = _tma_ready(q), _tma_ready(k), _tma_ready(v), _tma_ready(do.to(q.dtype))
+    dr = dr.to(q.dtype).contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ends = _strip(cu_seqlens, leading_zero)
+    if _compiling():
+        _op_varlen_bwd(do, dr, q, k, v, ends, 0 if max_seqlens is None else int(max_seqlens), log_rem,
+                       float(logit_scale), bool(attend_current), bool(leading_zero), dq, dk, dv)
+    else:
+        _bwd_impl(False, do, dr, q, k, v, ends, max_seqlens, log_rem, logit_scale, attend_current,
+                  leading_zero, dq, dk, dv)
+    return dq, dk, dv
+
+
+def attn_fwd(q, k, v, logit_scale: float, attend_current: bool = False):
+    """Fixed-length ``(B,H,T,d)`` forward; returns ``(o, rem, log_rem)``."""
+    q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+    o = torch.empty_like(q)
+    rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
+    log_rem = torch.empty(q.shape[:-1], dtype=torch.float64, device=q.device)
+    if _compiling():
+        _op_attn_fwd(q, k, v, float(logit_scale), bool(attend_current), o, rem, log_rem)
+    else:
+        _fwd_impl(True, q, k, v, None, None, logit_scale, attend_current, False, o, rem, log_rem)
+    return o, rem, log_rem
+
+
+def attn_bwd(do, dr, q, k, v, log_rem, logit_scale: float, attend_current: bool = False):
+    """Fixed-length backward; returns ``(dq, dk, dv)`` in the dtype of the inputs (the reference
+    forces dk and dv to bf16 here, ``sb_attn/sb_bwd.py:173-174``; this keeps the input dtype)."""
+    q, k, v, do = _tma_ready(q), _tma_ready(k), _tma_ready(v), _tma_ready(do.to(q.dtype))
+    dr = dr.to(q.dtype).contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if _compiling():
+        _op_attn_bwd(do, dr, q, k, v, log_rem, float(logit_scale), bool(attend_current), dq, dk, dv)
+    else:
+        _bwd_impl(True, do, dr, q, k, v, None, None, log_rem, logit_scale, attend_current, False, dq, dk, dv)
+    return dq, dk, dv
+
+
+def kernel_path(q, fixed: bool = False) -> int:
+    """Which kernels a call with tensors like ``q`` takes: 0 = CUDA cores, 1 = tcgen05."""
+    prm = _cabi.SbParams()
+    dummy_cu = None if fixed else torch.zeros(1, dtype=torch.int32, device=q.device)
+    _fill(prm, fixed=fixed, q=q, k=q, v=q, cu_seqlens=dummy_cu, max_seqlens=None, logit_scale=1.0,
+          attend_current=False, leading_zero=False)
+    return _cabi.load().sb_kernel_path(prm)

@@ -1,0 +1,41 @@
+"""``sb_attn``: stick-breaking attention over a fixed-length ``(batch, heads, tokens, head_dim)`` batch.
+
+Drop-in for ``stickbreaking_attention.sb_attn.sb_attn`` (``sb_attn/__init__.py:16-64``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import ops
+
+
+class StickBreakingAttention(torch.autograd.Function):
+    """Autograd glue of the fixed-length operator (reference: ``sb_attn/__init__.py:16-54``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, inv_temp, attend_current=False):
+        o, rem, log_rem = ops.attn_fwd(q, k, v, inv_temp, attend_current=attend_current)
+        ctx.save_for_backward(q, k, v, log_rem)
+        ctx.logit_scale = inv_temp
+        ctx.attend_current = attend_current
+        return o, rem
+
+    @staticmethod
+    def backward(ctx, do, drem):
+        q, k, v, log_rem = ctx.saved_tensors
+        dq, dk, dv = ops.attn_bwd(do, drem, q, k, v, log_rem, ctx.logit_scale,
+                                  attend_current=ctx.attend_current)
+        return dq, dk, dv, None, None
+
+
+def sb_attn(q, k, v, inv_temp=None, zero_start=True, attend_current=False):
+    """``zero_start`` is accepted and ignored, as in the reference (``sb_attn/__init__.py:57``)."""
+    if inv_temp is None:
+        inv_temp = 1 / math.sqrt(q.size(-1))
+    return sb_attn_(q, k, v, inv_temp, attend_current=attend_current)
+
+
+def sb_attn_(q, k, v, inv_temp, attend_current):
+    return StickBreakingAttention.apply(q, k, v, inv_temp, attend_current)

@@ -1,0 +1,83 @@
+"""Shared helpers of the GPU parity tests: run the CUDA path and the CPU oracle on the same inputs."""
+import math
+
+import torch
+
+from oracle import sb_oracle as O
+
+# Tolerances of the path (stated by the build target): against the oracle run in fp32 on the same
+# seeded inputs, bf16/fp16 I/O within 2e-2 max-abs on o and rem and 5e-2 relative L2 on dq/dk/dv;
+# fp32 I/O within 1e-4 on everything.
+TOL = {
+    torch.float32: dict(out=1e-4, grad_rel=1e-4),
+    torch.bfloat16: dict(out=2e-2, grad_rel=5e-2),
+    torch.float16: dict(out=2e-2, grad_rel=5e-2),
+}
+
+
+def make_inputs(shape, dtype, seed, recipe="normal", std=1.0):
+    """'normal': N(0, std^2); 'reference': the reference tests' shifted recipe (tests/test_varlen.py:83-89)."""
+    gen = torch.Generator().manual_seed(seed)
+    if recipe == "reference":
+        v = 0.25 * torch.randn(shape, generator=gen)
+        q = 0.25 * (torch.randn(shape, generator=gen) + 1)
+        k = 0.25 * (torch.randn(shape, generator=gen) - 1)
+    else:
+        q, k, v = (std * torch.randn(shape, generator=gen) for _ in range(3))
+    do = torch.randn(shape, generator=gen)
+    drem = torch.randn(shape[:-1], generator=gen)
+    return tuple(t.to(dtype) for t in (q, k, v, do, drem))
+
+
+def rel_l2(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-20))
+
+
+def max_abs(a, b):
+    return float((a.double().cpu() - b.double().cpu()).abs().max()) if a.numel() else 0.0
+
+
+def run_varlen(sb, q, k, v, do, drem, cu, device, *, zero_start=False, max_seqlens=None, inv_temp=None,
+               attend_current=False):
+    qd, kd, vd = (t.to(device).requires_grad_(True) for t in (q, k, v))
+    o, rem = sb.sb_attn_varlen(qd, kd, vd, cu.to(device), max_seqlens, inv_temp=inv_temp,
+                               zero_start=zero_start, attend_current=attend_current)
+    dq, dk, dv = torch.autograd.grad((o, rem), (qd, kd, vd), (do.to(device), drem.to(device)))
+    return tuple(t.detach().cpu() for t in (o, rem, dq, dk, dv))
+
+
+def run_fixed(sb, q, k, v, do, drem, device, *, inv_temp=None, attend_current=False):
+    qd, kd, vd = (t.to(device).requires_grad_(True) for t in (q, k, v))
+    o, rem = sb.sb_attn(qd, kd, vd, inv_temp=inv_temp, attend_current=attend_current)
+    dq, dk, dv = torch.autograd.grad((o, rem), (qd, kd, vd), (do.to(device), drem.to(device)))
+    return tuple(t.detach().cpu() for t in (o, rem, dq, dk, dv))
+
+
+def oracle_varlen(q, k, v, do, drem, cu, *, zero_start=False, inv_temp=None, attend_current=False):
+    f = lambda t: t.float()
+    lengths = O.seq_bounds(cu, zero_start)
+    if max(e - s for s, e in lengths) <= 2048:
+        return O.varlen_dense_grads(f(q), f(k), f(v), cu, f(do), f(drem), scale=inv_temp,
+                                    attend_current=attend_current, zero_start=zero_start)
+    return O.varlen_rowblocked_grads(f(q), f(k), f(v), cu, f(do), f(drem), scale=inv_temp,
+                                     attend_current=attend_current, zero_start=zero_start)
+
+
+def oracle_fixed(q, k, v, do, drem, *, inv_temp=None, attend_current=False):
+    f = lambda t: t.float()
+    return O.fixed_dense_grads(f(q), f(k), f(v), f(do), f(drem), scale=inv_temp, attend_current=attend_current)
+
+
+def assert_parity(got, want, dtype, what=""):
+    tol = TOL[dtype]
+    names = ("o", "rem", "dq", "dk", "dv")
+    report = {}
+    for name, a, b in zip(names, got, want):
+        assert torch.isfinite(a.float()).all(), f"{what}: {name} has non-finite values"
+        report[name] = (max_abs(a, b), rel_l2(a, b))
+    for name in ("o", "rem"):
+        assert report[name][0] <= tol["out"], f"{what}: {name} max-abs {report[name][0]:.3e} > {tol['out']}"
+    for name in ("dq", "dk", "dv"):
+        assert report[name][1] <= tol["grad_rel"], f"{what}: {name} rel-L2 {report[name][1]:.3e} > {tol['grad_rel']}"
+    return report

@@ -1,0 +1,231 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the reference's golden vectors."""
+import math
+
+import pytest
+import torch
+
+from conftest import load_golden
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.fixture(scope="module")
+def sb(cuda_device):
+    import stickbreaking_attention_b200 as sb
+    yield sb
+    sb.check_status(cuda_device)
+
+
+def cu_of(lengths, zero_start=False, dtype=torch.int64):
+    ends = torch.tensor(lengths, dtype=dtype).cumsum(0).to(dtype)
+    return torch.cat([torch.zeros(1, dtype=dtype), ends]) if zero_start else ends
+
+
+# ---- golden vectors produced by the reference itself -------------------------------------------------
+
+@pytest.mark.parametrize("ac", [0, 1])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_golden_tiny_varlen(sb, cuda_device, ac, dtype):
+    g = load_golden(f"tiny_varlen_ac{ac}")
+    ins = [g[n].to(dtype) for n in ("q", "k", "v", "do", "drem")]
+    got = H.run_varlen(sb, *ins, cu_of(g["lengths"]), cuda_device, attend_current=bool(ac))
+    if dtype == torch.float32:
+        want = [g[n] for n in ("o", "rem", "dq", "dk", "dv")]
+    else:   # the stored vectors are for the unrounded inputs; re-run the oracle on the rounded ones
+        want = H.oracle_varlen(*ins, cu_of(g["lengths"]), attend_current=bool(ac))
+    H.assert_parity(got, want, dtype, "tiny_varlen")
+
+
+@pytest.mark.parametrize("ac", [0, 1])
+def test_golden_tiny_fixed_fp32(sb, cuda_device, ac):
+    g = load_golden(f"tiny_fixed_ac{ac}")
+    ins = [g[n] for n in ("q", "k", "v", "do", "drem")]
+    got = H.run_fixed(sb, *ins, cuda_device, attend_current=bool(ac))
+    H.assert_parity(got, [g[n] for n in ("o", "rem", "dq", "dk", "dv")], torch.float32, "tiny_fixed")
+
+
+@pytest.mark.parametrize("ac", [0, 1])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_golden_reference_recipe(sb, cuda_device, ac, dtype):
+    """bf16-representable inputs (d=128): the bf16 tensor-core path and the fp32 path see exactly the
+    inputs the reference oracle saw."""
+    g = load_golden(f"recipe_varlen_ac{ac}")
+    ins = [g[n].to(dtype) for n in ("q", "k", "v", "do", "drem")]
+    got = H.run_varlen(sb, *ins, cu_of(g["lengths"]), cuda_device, attend_current=bool(ac))
+    H.assert_parity(got, [g[n] for n in ("o", "rem", "dq", "dk", "dv")], dtype, "recipe")
+
+
+def test_golden_c1_config(sb, cuda_device):
+    """BASELINE config 1: H=4, d=64, lengths [128,256,64,512], seed 0, fp32, zero_start=False."""
+    g = load_golden("c1")
+    torch.manual_seed(0)
+    shape = (4, 960, 64)
+    q, k, v, do = (torch.randn(shape) for _ in range(4))
+    drem = torch.randn(shape[:2])
+    got = H.run_varlen(sb, q, k, v, do, drem, cu_of(g["lengths"]), cuda_device, inv_temp=1 / 8)
+    stride = int(g["row_stride"])
+    H.assert_parity([t[:, ::stride] for t in got], [g[n] for n in ("o", "rem", "dq", "dk", "dv")],
+                    torch.float32, "c1")
+
+
+# ---- seeded inputs against the oracle -------------------------------------------------------------------
+
+RAGGED = [1, 2, 63, 64, 65, 127, 128, 129, 31, 300]
+
+
+@pytest.mark.parametrize("ac", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [64, 128])
+def test_varlen_ragged(sb, cuda_device, dtype, d, ac):
+    ins = H.make_inputs((3, sum(RAGGED), d), dtype, seed=d + int(ac))
+    cu = cu_of(RAGGED)
+    got = H.run_varlen(sb, *ins, cu, cuda_device, attend_current=ac, max_seqlens=max(RAGGED))
+    H.assert_parity(got, H.oracle_varlen(*ins, cu, attend_current=ac), dtype, "ragged")
+    if not ac:   # first token of each sequence attends to nothing
+        starts = [0] + cu.tolist()[:-1]
+        assert torch.all(got[0][:, starts] == 0) and torch.all(got[1][:, starts] == 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_varlen_forms_agree(sb, cuda_device, dtype):
+    """zero_start / int32 / missing max_seqlens / empty sequences are the same computation."""
+    lengths = [40, 0, 200, 17]
+    ins = H.make_inputs((2, sum(lengths), 64), dtype, seed=3)
+    base = H.run_varlen(sb, *ins, cu_of(lengths), cuda_device, max_seqlens=200)
+    H.assert_parity(base, H.oracle_varlen(*ins, cu_of([40, 200, 17])), dtype, "forms")
+    for kwargs, cu in [(dict(zero_start=True), cu_of(lengths, True)),
+                       (dict(zero_start=True, max_seqlens=256), cu_of(lengths, True, torch.int32)),
+                       (dict(max_seqlens=None), cu_of(lengths, dtype=torch.int32))]:
+        other = H.run_varlen(sb, *ins, cu, cuda_device, **kwargs)
+        for a, b in zip(base, other):
+            assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_tokens_after_last_sequence_are_zero(sb, cuda_device, dtype):
+    lengths = [70, 50]
+    ins = H.make_inputs((2, 150, 64), dtype, seed=4)
+    got = H.run_varlen(sb, *ins, cu_of(lengths), cuda_device)
+    want = H.oracle_varlen(*[t[:, :120] for t in ins], cu_of(lengths))
+    H.assert_parity([t[:, :120] for t in got], want, dtype, "tail")
+    for t in got:
+        assert torch.all(t[:, 120:] == 0)
+
+
+@pytest.mark.parametrize("ac", [False, True])
+@pytest.mark.parametrize("shape", [(2, 3, 256, 64), (1, 7, 500, 50), (2, 2, 512, 32), (1, 2, 300, 16),
+                                   (1, 2, 1024, 128), (4, 1, 130, 128)])
+def test_fixed_reference_grid_bf16(sb, cuda_device, shape, ac):
+    """Shapes drawn from the reference's own test grid (tests/test_attn.py:37-43) with its input
+    recipe, checked the way it checks (o + rem*v and its gradients, max-abs < 0.05) and to this
+    build's tighter tolerances."""
+    dtype = torch.bfloat16
+    q, k, v, do, _ = H.make_inputs(shape, dtype, seed=1337, recipe="reference")
+    drem = (do.float() * v.float()).sum(-1).to(dtype)         # d(o + rem*v)/d rem
+    got = H.run_fixed(sb, q, k, v, do, drem, cuda_device, attend_current=ac)
+    want = H.oracle_fixed(q, k, v, do, drem, attend_current=ac)
+    H.assert_parity(got, want, dtype, f"fixed{shape}")
+    folded = got[0].float() + got[1].float()[..., None] * v.float()
+    folded_ref = want[0] + want[1][..., None] * v.float()
+    assert H.max_abs(folded, folded_ref) < 0.05
+    for a, b in zip(got[2:4], want[2:4]):
+        assert H.max_abs(a, b) < 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_fixed_matches_varlen_layout(sb, cuda_device, dtype):
+    """(B,H,T,d) through sb_attn == the same sequences packed through sb_attn_varlen, bitwise."""
+    B, Hh, T, d = 3, 2, 192, 128
+    q, k, v, do, drem = H.make_inputs((B, Hh, T, d), dtype, seed=9)
+    fixed = H.run_fixed(sb, q, k, v, do, drem, cuda_device)
+    pack = lambda t: t.transpose(0, 1).reshape(Hh, B * T, *t.shape[3:])
+    packed = H.run_varlen(sb, *(pack(t) for t in (q, k, v, do, drem)), cu_of([T] * B), cuda_device)
+    for a, b in zip(fixed, packed):
+        assert torch.equal(pack(a), b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_strided_views_and_scale(sb, cuda_device, dtype):
+    """(T,H,d) storage viewed as (H,T,d), as the reference benchmarks pass it
+    (benchmarks/varlen.py:43-45), and a non-default inv_temp."""
+    lengths = [100, 156]
+    T, Hh, d = 256, 3, 64
+    gen = torch.Generator().manual_seed(5)
+    q, k, v, do = (torch.randn(T, Hh, d, generator=gen).to(dtype).permute(1, 0, 2) for _ in range(4))
+    drem = torch.randn(Hh, T, generator=gen).to(dtype)
+    got = H.run_varlen(sb, q, k, v, do, drem, cu_of(lengths), cuda_device, inv_temp=0.2)
+    want = H.oracle_varlen(q, k, v, do, drem, cu_of(lengths), inv_temp=0.2)
+    H.assert_parity(got, want, dtype, "strided")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_backward_is_bitwise_deterministic(sb, cuda_device, dtype):
+    lengths = [700, 324]
+    ins = H.make_inputs((4, 1024, 128), dtype, seed=6)
+    a = H.run_varlen(sb, *ins, cu_of(lengths), cuda_device)
+    b = H.run_varlen(sb, *ins, cu_of(lengths), cuda_device)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_long_sequence_bf16(sb, cuda_device):
+    """One 4096-token sequence, d=128 (the reference's varlen test shape, tests/test_varlen.py:68-74)."""
+    dtype = torch.bfloat16
+    q, k, v, do, _ = H.make_inputs((3, 4096, 128), dtype, seed=1337, recipe="reference")
+    drem = (do.float() * v.float()).sum(-1).to(dtype)
+    cu = cu_of([4096])
+    got = H.run_varlen(sb, q, k, v, do, drem, cu, cuda_device, max_seqlens=4096)
+    want = H.oracle_varlen(q, k, v, do, drem, cu)
+    H.assert_parity(got, want, dtype, "L4096")
+
+
+def test_tensor_core_path_is_taken(sb, cuda_device):
+    """bf16/fp16 with head_dim 64 or 128 must run the tcgen05 kernels, fp32 the CUDA-core ones."""
+    for d in (64, 128):
+        for dtype in (torch.bfloat16, torch.float16):
+            assert sb.kernel_path(torch.empty(2, 256, d, dtype=dtype, device=cuda_device)) == 1
+    assert sb.kernel_path(torch.empty(2, 256, 64, dtype=torch.float32, device=cuda_device)) == 0
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_tensor_core_and_cuda_core_paths_agree(sb, cuda_device, d):
+    dtype = torch.bfloat16
+    lengths = [257, 640, 127]
+    ins = H.make_inputs((2, sum(lengths), d), dtype, seed=8)
+    fast = H.run_varlen(sb, *ins, cu_of(lengths), cuda_device)
+    with sb.force_simt():
+        slow = H.run_varlen(sb, *ins, cu_of(lengths), cuda_device)
+    for name, a, b in zip(("o", "rem"), fast, slow):
+        assert H.max_abs(a, b) <= 2e-2, name
+    for name, a, b in zip(("dq", "dk", "dv"), fast[2:], slow[2:]):
+        assert H.rel_l2(a, b) <= 5e-2, name
+
+
+# ---- error behaviour: failures are made on the host, never by faulting the device -----------------------
+
+def test_bad_cu_seqlens_is_reported_not_executed(sb, cuda_device):
+    q = torch.randn(2, 64, 64, device=cuda_device)
+    sb.check_status(cuda_device)
+    for cu, kwargs in [(torch.tensor([40, 30]), dict(zero_start=False)),          # decreasing
+                       (torch.tensor([40, 100]), dict(zero_start=False)),         # beyond the tokens
+                       (torch.tensor([5, 40, 64]), dict(zero_start=True)),        # leading element not 0
+                       (torch.tensor([40, 64]), dict(zero_start=False, max_seqlens=30))]:
+        o, rem = sb.sb_attn_varlen(q, q, q, cu.to(cuda_device), **kwargs)
+        with pytest.raises(sb._cabi.SbError):
+            sb.check_status(cuda_device)
+    sb.check_status(cuda_device)   # cleared
+
+
+def test_argument_errors(sb, cuda_device):
+    q = torch.randn(2, 64, 64, device=cuda_device)
+    with pytest.raises(ValueError):
+        sb.sb_attn_varlen(q.cpu(), q.cpu(), q.cpu(), torch.tensor([64]))
+    with pytest.raises(ValueError):
+        sb.sb_attn_varlen(q, q[:, :32], q, torch.tensor([64], device=cuda_device), zero_start=False)
+    with pytest.raises(ValueError):
+        sb.sb_attn_varlen(q.double(), q.double(), q.double(), torch.tensor([64], device=cuda_device), zero_start=False)
+    with pytest.raises(ValueError):
+        sb.sb_attn(q, q, q)
