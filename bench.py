@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the stick-breaking attention hot path: sb_attn_varlen forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2s|c3|c4|c5]
+
+One step = one forward + backward pass of ``sb_attn_varlen`` over one synthetic batch.  The default
+workload is the configuration the headline metric is quoted on: 16 heads, head_dim 128, 8 sequences of
+2048 tokens (16384 packed tokens), q/k/v ~ N(0,1) in bf16, dO ~ N(0,1).  With N > 1 (one process per
+GPU under torchrun) every rank runs its own batch of that shape: the path shards by independent
+(head, sequence) pairs with no collective, so scaling is "weak" and ``value`` is the sum over ranks of
+the algorithmic FLOPs divided by the slowest rank's device time.
+
+Printed by rank 0, one JSON line:
+  value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e        same metric through the public Python operator with pinned HOST buffers: the H2D copies of
+             q, k, v, dO, dRem and the D2H copies of o, rem, dq, dk, dv are inside the timed region
+  roofline   the dominant kernel against the measured dense bf16 tensor peak
+  cpu_baseline  the CPU oracle (a port of the reference's sb_ref) on a bounded sample, rank 0, N == 1
+
+FLOP convention (causal): forward 2*L^2*d per head per sequence, backward 2.5x that.
+
+``--impl reference`` times the reference's CPU algorithm (the oracle port; the reference itself is a
+Python package that does not travel to the GPU box) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
+
+
+# ---------------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------------
+def workload(name: str, seed: int = 0):
+    """Returns dict(heads, head_dim, lengths, std, zero_start, fwd_only, label)."""
+    import numpy as np
+    if name == "c2":
+        return dict(heads=16, head_dim=128, lengths=[2048] * 8, std=1.0, zero_start=False, fwd_only=False,
+                    label="16 heads x 8 sequences x 2048 tokens, head_dim 128, bf16, fwd+bwd")
+    if name == "c2s":     # small stand-in used for profiler captures
+        return dict(heads=8, head_dim=128, lengths=[2048] * 4, std=1.0, zero_start=False, fwd_only=False,
+                    label="8 heads x 4 sequences x 2048 tokens, head_dim 128, bf16, fwd+bwd")
+    if name == "c3":
+        rng = np.random.default_rng(seed)
+        lengths, total = [], 0
+        while total < 65536:
+            n = int(np.clip(rng.lognormal(np.log(1024.0), 1.0), 64, 16384))
+            n = min(n, 65536 - total)
+            lengths.append(n)
+            total += n
+        return dict(heads=32, head_dim=128, lengths=lengths, std=1.0, zero_start=True, fwd_only=False,
+                    label="32 heads, 65536 tokens in lognormal-length sequences, head_dim 128, bf16, fwd+bwd")
+    if name == "c4":
+        return dict(heads=16, head_dim=128, lengths=[131072], std=0.5, zero_start=False, fwd_only=False,
+                    label="16 heads x 1 sequence of 131072 tokens, head_dim 128, bf16, fwd+bwd")
+    if name == "c5":
+        rng = np.random.default_rng(seed)
+        lengths = rng.integers(128, 513, size=4096).tolist()
+        return dict(heads=32, head_dim=64, lengths=lengths, std=1.0, zero_start=False, fwd_only=True,
+                    label="32 heads, 4096 sequences of 128..512 tokens, head_dim 64, bf16, forward only")
+    raise SystemExit(f"unknown workload {name}")
+
+
+def flops_of(w, mode):
+    c = {"fwd": 2.0, "bwd": 5.0, "fwd_bwd": 7.0}[mode]
+    return c * w["head_dim"] * w["heads"] * float(sum(n * n for n in w["lengths"]))
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            data = json.load(f)
+        return {"bf16_tflops": float(data["bf16_tflops"]), "hbm_gbs": float(data["hbm_gbs"]),
+                "bf16_tflops_sustained": float(data.get("bf16_tflops_sustained", data["bf16_tflops"]))}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------------------------
+# clock sampling (read-only NVML queries)
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                bits = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's algorithm on the host cores
+# ---------------------------------------------------------------------------------------------------
+def cpu_sample(w, heads, seqs, reps):
+    """Times forward+backward of the oracle on `heads` heads x the first `seqs` sequences; returns
+    (best seconds, TFLOP/s under the causal convention, description)."""
+    from oracle import sb_oracle as O
+    lengths = w["lengths"][:seqs]
+    gen = torch.Generator().manual_seed(0)
+    shape = (heads, sum(lengths), w["head_dim"])
+    q, k, v = (w["std"] * torch.randn(shape, generator=gen) for _ in range(3))
+    do = torch.randn(shape, generator=gen)
+    drem = torch.randn(shape[:2], generator=gen)
+    cu = torch.tensor(lengths).cumsum(0)
+    fn = O.varlen_dense_grads if max(lengths) <= 4096 else O.varlen_rowblocked_grads
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn(q, k, v, cu, do, drem)
+        best = min(best, time.perf_counter() - t0)
+    fl = 7.0 * w["head_dim"] * heads * float(sum(n * n for n in lengths))
+    desc = (f"{heads} heads x first {seqs} sequence(s) ({sum(lengths)} tokens) of the workload, fp32, "
+            f"forward + autograd backward, best of {reps}")
+    return best, fl / best / 1e12, desc
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = torch.get_num_threads()
+    heads, seqs = min(4, w["heads"]), 1
+    times = []
+    tfl = 0.0
+    desc = ""
+    for i in range(args.warmup + args.steps):
+        sec, tfl_i, desc = cpu_sample(w, heads, seqs, 1)
+        if i >= args.warmup:
+            times.append(sec)
+            tfl = max(tfl, tfl_i)
+    mean = sum(times) / len(times)
+    fl = 7.0 * w["head_dim"] * heads * float(sum(n * n for n in w["lengths"][:seqs]))
+    value = fl / mean / 1e12
+    line = {
+        "impl": "reference", "metric": "sb_attn_varlen fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["label"], "sample_per_step": desc, "host_cores": os.cpu_count(),
+                   "torch_threads": threads},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def make_batch(w, device, seed):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    T = sum(w["lengths"])
+    shape = (w["heads"], T, w["head_dim"])
+    host = {}
+    for name in ("q", "k", "v"):
+        host[name] = (w["std"] * torch.randn(shape, generator=gen)).to(torch.bfloat16).pin_memory()
+    host["do"] = torch.randn(shape, generator=gen).to(torch.bfloat16).pin_memory()
+    host["drem"] = torch.randn(shape[:2], generator=gen).to(torch.bfloat16).pin_memory()
+    ends = torch.tensor(w["lengths"], dtype=torch.int32).cumsum(0).to(torch.int32)
+    cu = torch.cat([torch.zeros(1, dtype=torch.int32), ends]) if w["zero_start"] else ends
+    return host, cu.to(device)
+
+
+def event_time_ms(fn, iters):
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iters
+
+
+def kernel_breakdown(sb, w, dev_t, cu, max_len, iters=5):
+    """Average device time of each kernel group, timed alone through the C ABI with CUDA events on the
+    launching stream: forward, backward dQ kernel, backward dK/dV kernel."""
+    from stickbreaking_attention_b200 import _cabi, ops
+    lib = _cabi.load()
+    q, k, v, do, drem = (dev_t[n] for n in ("q", "k", "v", "do", "drem"))
+    ends = cu[1:] if w["zero_start"] else cu
+    o = torch.empty_like(q)
+    rem = torch.empty(q.shape[:2], dtype=q.dtype, device=q.device)
+    log_rem = torch.empty(q.shape[:2], dtype=torch.float64, device=q.device)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    status = torch.zeros(4, dtype=torch.int32, device=q.device)
+    prm = _cabi.SbParams()
+    ops._fill(prm, fixed=False, q=q, k=k, v=v, cu_seqlens=ends, max_seqlens=max_len,
+              logit_scale=w["head_dim"] ** -0.5, attend_current=False, leading_zero=w["zero_start"])
+    prm.o = _cabi.tensor_arg(o, False)
+    prm.rem, prm.log_rem = rem.data_ptr(), log_rem.data_ptr()
+    prm.d_o = _cabi.tensor_arg(do, False)
+    prm.d_rem = drem.data_ptr()
+    prm.dq, prm.dk, prm.dv = (_cabi.tensor_arg(t, False) for t in (dq, dk, dv))
+    need = max(lib.sb_workspace_bytes(prm, 1), lib.sb_workspace_bytes(prm, 0))
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    prm.workspace, prm.workspace_bytes, prm.status = ws.data_ptr(), ws.numel(), status.data_ptr()
+    stream = torch.cuda.current_stream().cuda_stream
+    base_flags = prm.flags
+
+    def call(fn, flags):
+        prm.flags = base_flags | flags
+        rc = fn(prm, stream)
+        if rc != 0:
+            raise RuntimeError(lib.sb_last_error().decode())
+
+    call(lib.sb_fwd, 0)
+    call(lib.sb_bwd, 0)
+    torch.cuda.synchronize()
+    out = {"fwd": event_time_ms(lambda: call(lib.sb_fwd, 0), iters)}
+    if not w["fwd_only"]:
+        out["bwd_dq"] = event_time_ms(lambda: call(lib.sb_bwd, _cabi.SB_FLAG_BWD_SKIP_DKV), iters)
+        out["bwd_dkv"] = event_time_ms(lambda: call(lib.sb_bwd, _cabi.SB_FLAG_BWD_SKIP_DQ), iters)
+    path = lib.sb_kernel_path(prm)
+    return out, path
+
+
+def run_gpu_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    distributed = world > 1
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    import stickbreaking_attention_b200 as sb
+
+    host, cu = make_batch(w, device, seed=1234 + rank)
+    dev_t = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+    max_len = max(w["lengths"])
+    fwd_only = w["fwd_only"]
+    mode = "fwd" if fwd_only else "fwd_bwd"
+
+    def step_resident():
+        q, k, v = (dev_t[n].requires_grad_(not fwd_only) for n in ("q", "k", "v"))
+        o, rem = sb.sb_attn_varlen(q, k, v, cu, max_len, zero_start=w["zero_start"])
+        if fwd_only:
+            return o, rem
+        return torch.autograd.grad((o, rem), (q, k, v), (dev_t["do"], dev_t["drem"]))
+
+    out_host = {}
+
+    def step_e2e():
+        q, k, v, do, drem = (host[n].to(device, non_blocking=True) for n in ("q", "k", "v", "do", "drem"))
+        q, k, v = (t.requires_grad_(not fwd_only) for t in (q, k, v))
+        o, rem = sb.sb_attn_varlen(q, k, v, cu, max_len, zero_start=w["zero_start"])
+        results = {"o": o, "rem": rem}
+        if not fwd_only:
+            dq, dk, dv = torch.autograd.grad((o, rem), (q, k, v), (do, drem))
+            results.update(dq=dq, dk=dk, dv=dv)
+        for name, t in results.items():
+            if name not in out_host:
+                out_host[name] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            out_host[name].copy_(t.detach(), non_blocking=True)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step, steps, warmup):
+        for _ in range(warmup):
+            step()
+        barrier()
+        launches0 = sb.kernel_launches()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record()
+            for _ in range(steps):
+                step()
+            stop.record()
+            barrier()
+        ms = start.elapsed_time(stop)
+        if distributed:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, sb.kernel_launches() - launches0, clocks.summary()
+
+    ms_step, launches, clocks = timed(step_resident, args.steps, max(args.warmup, 3))
+    sb.check_status(device)
+    e2e_steps = max(3, min(args.steps, 20))
+    ms_e2e, _, _ = timed(step_e2e, e2e_steps, 3)
+
+    fl = flops_of(w, mode)
+    value = fl * world / (ms_step * 1e-3) / 1e12
+    e2e_value = fl * world / (ms_e2e * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in out_host.values())
+
+    line = None
+    if rank == 0:
+        peaks, peak_kind = load_peaks()
+        kern, path = kernel_breakdown(sb, w, dev_t, cu, max_len)
+        alg = {"fwd": flops_of(w, "fwd"), "bwd_dq": 0.6 * flops_of(w, "bwd"), "bwd_dkv": 0.4 * flops_of(w, "bwd")}
+        kernels = {name: {"ms": ms, "tflops": alg[name] / (ms * 1e-3) / 1e12} for name, ms in kern.items()}
+        top = max(kern, key=lambda n: kern[n])
+        achieved = kernels[top]["tflops"]
+        roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                    "peak_source": f"{peak_kind} dense bf16 (burst)", "kernels": kernels,
+                    "step_frac_of_peak": value / world / peaks["bf16_tflops"],
+                    "kernel_path": "tcgen05" if path == 1 else "cuda-core"}
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            heads = min(8, w["heads"])
+            sec, tfl, desc = cpu_sample(w, heads, 1, 3)
+            cpu = {"value": tfl, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                   "sample": desc, "seconds": sec, "host_cores": os.cpu_count()}
+        line = {
+            "metric": "sb_attn_varlen fwd+bwd TFLOP/s" if not fwd_only else "sb_attn_varlen fwd TFLOP/s",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["label"], "name": args.workload, "tokens_per_gpu": sum(w["lengths"]),
+                       "sequences_per_gpu": len(w["lengths"]), "heads": w["heads"], "head_dim": w["head_dim"],
+                       "parallelism": f"{world} independent shard(s), no collective",
+                       "l2": "q,k,v,dO and the outputs of one step exceed the 126 MB L2; no flush between steps",
+                       "flop_convention": "causal: fwd 2*L^2*d per head per sequence, bwd 2.5x"},
+            "tokens_per_s": sum(w["lengths"]) * world / (ms_step * 1e-3),
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+        }
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = workload(args.workload)
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_gpu_arm(args, w)
+
+
+if __name__ == "__main__":
+    main()
