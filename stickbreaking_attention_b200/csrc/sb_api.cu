@@ -50,7 +50,7 @@ static bool tma_friendly(const SbTensor &t, int esize) {
   return t.stride_t % m == 0 && t.stride_h % m == 0 && t.stride_b % m == 0 && t.stride_t > 0;
 }
 
-static int make_plan(const SbParams *p, Plan &pl) {
+static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   if (p == nullptr) return fail(SB_ERR_ARGUMENT, "params is NULL");
   if (p->struct_bytes != (int)sizeof(SbParams))
     return fail(SB_ERR_ARGUMENT, "struct_bytes %d != sizeof(SbParams) %d", p->struct_bytes, (int)sizeof(SbParams));
@@ -67,8 +67,12 @@ static int make_plan(const SbParams *p, Plan &pl) {
   if (p->max_seqlen < 0) return fail(SB_ERR_ARGUMENT, "max_seqlen is negative");
 
   const int esize = p->dtype == SB_DTYPE_F32 ? 4 : 2;
-  const bool tc = !(p->flags & SB_FLAG_FORCE_SIMT) && tc_supported(p->dtype, p->head_dim) &&
-                  tma_friendly(p->q, esize) && tma_friendly(p->k, esize) && tma_friendly(p->v, esize);
+  bool tc = !(p->flags & SB_FLAG_FORCE_SIMT) && tc_supported(p->dtype, p->head_dim, backward) &&
+            tma_friendly(p->q, esize) && tma_friendly(p->k, esize) && tma_friendly(p->v, esize);
+  // outputs and gradients are stored with 16-byte vectors on the tensor-core path
+  const SbTensor *others[] = {&p->o, &p->d_o, &p->dq, &p->dk, &p->dv};
+  for (const SbTensor *t : others)
+    if (t->ptr != nullptr && !tma_friendly(*t, esize)) tc = false;
   pl.path = tc ? SB_PATH_TCGEN05 : SB_PATH_SIMT;
   pl.tile = tc ? kTcTile : kSimtTile;
   const long long T = p->tokens;
@@ -169,7 +173,7 @@ static int run(const SbParams *p, void *stream, bool backward) {
   g_err[0] = 0;
   g_launches = 0;
   Plan pl;
-  int rc = make_plan(p, pl);
+  int rc = make_plan(p, pl, backward);
   if (rc) return rc;
   if ((rc = device_ok())) return rc;
   KParams k;
@@ -203,7 +207,7 @@ extern "C" {
 
 size_t sb_workspace_bytes(const SbParams *p, int backward) {
   sb::Plan pl;
-  if (sb::make_plan(p, pl)) return (size_t)-1;
+  if (sb::make_plan(p, pl, backward != 0)) return (size_t)-1;
   return backward ? pl.total_bwd : pl.total_fwd;
 }
 
@@ -213,7 +217,7 @@ int sb_bwd(const SbParams *p, void *stream) { return sb::run(p, stream, true); }
 
 int sb_kernel_path(const SbParams *p) {
   sb::Plan pl;
-  if (sb::make_plan(p, pl)) return -1;
+  if (sb::make_plan(p, pl, false)) return -1;
   return pl.path;
 }
 

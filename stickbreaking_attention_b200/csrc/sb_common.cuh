@@ -114,7 +114,7 @@ cudaError_t launch_simt_fwd(const KParams &p, int dtype, cudaStream_t s, int *la
 cudaError_t launch_simt_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
 cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
 cudaError_t launch_tc_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
-bool tc_supported(int dtype, int head_dim);
+bool tc_supported(int dtype, int head_dim, bool backward);
 
 constexpr int kSimtTile = 32;
 constexpr int kTcTile = 128;

@@ -41,12 +41,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait: gives up after roughly a second and returns false; the caller then records an error
 // status and leaves through the normal exit so that tensor memory is released.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int spin = 0; spin < 2048; ++spin)
+  for (int spin = 0; spin < 4096; ++spin)
     if (mbar_try_wait(bar, parity)) return true;
-  for (int spin = 0; spin < (1 << 22); ++spin) {
+  const uint64_t t0 = global_timer_ns();
+  for (int spin = 0; spin < (1 << 24); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(128);
+    if (global_timer_ns() - t0 > 1000000000ull) return false;
+    __nanosleep(64);
   }
   return false;
 }

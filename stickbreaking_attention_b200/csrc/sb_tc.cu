@@ -1,8 +1,349 @@
-// Tensor-core (tcgen05 + TMEM + TMA) kernels.  Placeholder until the kernels land.
+// Tensor-core kernels for bf16 / fp16 tensors: tcgen05 MMAs with TMEM accumulators, K/V tiles staged by TMA.
+//
+// Forward (reference counterpart: _forward_one_row, sb_varlen_fwd.py:81-215).  One CTA owns a 128-row query
+// tile of one (sequence, head) and walks the key tiles from the diagonal back to the sequence start:
+//   warp 4    TMA producer: Q once, then K and V tiles into a ring of shared-memory stages
+//   warp 5    MMA issuer:   S = Q K^T into one of two TMEM buffers, O += P V into a third
+//   warps 0-3 one thread per query row: reads its row of S from TMEM (32 columns at a time, last column
+//             first), turns z into p = 2^(z + suffix sum of log2(1-beta)) with a running fp32 sum carried in
+//             registers, writes P as bf16 into the swizzled shared-memory layout the MMA reads
+// Every wait on an mbarrier is bounded; a wait that gives up records SB_DEV_WAIT_TIMEOUT and all roles
+// leave through the common exit, which frees the tensor memory.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "sb_common.cuh"
+#include "sb_ptx.cuh"
 
 namespace sb {
-bool tc_supported(int, int) { return false; }
-cudaError_t launch_tc_fwd(const KParams &, int, cudaStream_t, int *) { return cudaErrorNotSupported; }
+
+using namespace ptx;
+
+constexpr int kBM = kTcTile;  // 128 query rows per CTA, 128 keys per tile
+constexpr int kFwdThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kBoxBytes = kBM * 64 * 2;  // one TMA box: 128 rows x 64 16-bit elements, 128-byte swizzled
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kStages = D == 128 ? 2 : 4;
+  static constexpr int kTileBytes = kBM * D * 2;
+  static constexpr int kPBytes = kBM * kBM * 2;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmem = 1024 + kTileBytes * (1 + 2 * kStages) + kPBytes + kBarBytes;
+};
+
+// barrier slots (8 bytes each) inside the barrier block
+enum { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 5, kBarSFull = 9, kBarSEmpty = 11, kBarPFull = 13, kBarPEmpty = 14,
+       kBarOFull = 15, kNumBars = 16 };
+
+struct Ctl {  // lives behind the barriers in shared memory
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag, const KParams &p,
+                                              int which) {
+  if (mbar_wait(bar, parity)) return true;
+  *abort_flag = 1;
+  if (p.status != nullptr) { p.status[0] = SB_DEV_WAIT_TIMEOUT; p.status[1] = which; }
+  return false;
+}
+
+template <bool kFp16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kFp16) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+}
+
+// Byte offset of the 16-byte chunk holding columns [c0, c0+8) of row r in a [128 x 128] 16-bit tile stored as
+// two [128 x 64] K-major blocks with the 128-byte swizzle (chunk index XOR row mod 8).
+__device__ __forceinline__ uint32_t sw128_chunk_offset(int r, int c0) {
+  const int kb = c0 >> 6, chunk = (c0 & 63) >> 3;
+  return kb * kBoxBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
+}
+
+template <int D, bool kFp16>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const KParams p) {
+  using Cfg = FwdCfg<D>;
+  constexpr int NS = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x, true, c)) return;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  const uint32_t sQ = base;
+  const uint32_t sK = sQ + Cfg::kTileBytes;
+  const uint32_t sV = sK + NS * Cfg::kTileBytes;
+  const uint32_t sP = sV + NS * Cfg::kTileBytes;
+  const uint32_t sBar = sP + Cfg::kPBytes;
+  uint8_t *gP = gbase + (sP - base);
+  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + kNumBars * 8);
+  volatile int *abort_flag = &ctl->abort;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = p.head0 + blockIdx.y;
+  const int I = c.idx;
+  const int n_tiles = I + 1;
+  const int row0 = (int)c.tok0 + I * kBM;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(kBarQ), 1);
+    for (int s = 0; s < NS; ++s) { mbar_init(bar(kBarKvFull + s), 1); mbar_init(bar(kBarKvEmpty + s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar(kBarSFull + s), 1); mbar_init(bar(kBarSEmpty + s), 4); }
+    mbar_init(bar(kBarPFull), 4);
+    mbar_init(bar(kBarPEmpty), 1);
+    mbar_init(bar(kBarOFull), 1);
+    ctl->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  const uint32_t tS[2] = {tmem, tmem + 128};
+  const uint32_t tO = tmem + 256;
+
+  if (warp == 4) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+      mbar_arrive_expect_tx(bar(kBarQ), Cfg::kTileBytes);
+      for (int kb = 0; kb < D / 64; ++kb)
+        tma_load_4d(sQ + kb * kBoxBytes, &tm_q, bar(kBarQ), kb * 64, row0, h, (int)c.boff);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j % NS;
+        if (j >= NS && !wait_or_abort(bar(kBarKvEmpty + st), ((j / NS) - 1) & 1, abort_flag, p, 10)) break;
+        if (*abort_flag) break;
+        const int krow = (int)c.tok0 + (I - j) * kBM;
+        mbar_arrive_expect_tx(bar(kBarKvFull + st), 2 * Cfg::kTileBytes);
+        for (int kb = 0; kb < D / 64; ++kb) {
+          tma_load_4d(sK + st * Cfg::kTileBytes + kb * kBoxBytes, &tm_k, bar(kBarKvFull + st), kb * 64, krow, h, (int)c.boff);
+          tma_load_4d(sV + st * Cfg::kTileBytes + kb * kBoxBytes, &tm_v, bar(kBarKvFull + st), kb * 64, krow, h, (int)c.boff);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = idesc_f16(kBM, kBM, kFp16, false, false);
+      constexpr uint32_t idesc_pv = idesc_f16(kBM, D, kFp16, false, true);
+      auto issue_s = [&](int j) {  // S[j & 1] = Q K_j^T
+        const uint32_t kaddr = sK + (j % NS) * Cfg::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
+          mma_f16_ss(tS[j & 1], smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(kaddr + off, 16, 1024), idesc_s,
+                     k > 0);
+        }
+        mma_commit(bar(kBarSFull + (j & 1)));
+      };
+      bool ok = wait_or_abort(bar(kBarQ), 0, abort_flag, p, 20) && wait_or_abort(bar(kBarKvFull), 0, abort_flag, p, 21);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) {
+          const int jn = j + 1;
+          ok = wait_or_abort(bar(kBarKvFull + jn % NS), (jn / NS) & 1, abort_flag, p, 22);
+          if (ok && jn >= 2) ok = wait_or_abort(bar(kBarSEmpty + (jn & 1)), ((jn >> 1) - 1) & 1, abort_flag, p, 23);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(jn);
+        }
+        ok = wait_or_abort(bar(kBarPFull), j & 1, abort_flag, p, 24);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t vaddr = sV + (j % NS) * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kBM / 16; ++ks) {   // 16 keys per MMA
+          const uint32_t aoff = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+          mma_f16_ss(tO, smem_desc_sw128(sP + aoff, 16, 1024), smem_desc_sw128(vaddr + ks * 2048, kBoxBytes, 1024),
+                     idesc_pv, (j > 0 || ks > 0));
+        }
+        mma_commit(bar(kBarKvEmpty + j % NS));
+        mma_commit(bar(kBarPEmpty));
+      }
+      if (ok) mma_commit(bar(kBarOFull));
+    }
+  } else {
+    // ------------------------------------------------ one thread per query row
+    const int r = threadIdx.x;                       // row inside the tile == TMEM lane
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float scale2 = p.scale * kLog2e;
+    const int ac = p.attend_current;
+    double run = 0.0;                                // sum of log2(1+2^x) over the key tiles already visited
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      ok = wait_or_abort(bar(kBarSFull + (j & 1)), (j >> 1) & 1, abort_flag, p, 30);
+      if (ok && j > 0) ok = wait_or_abort(bar(kBarPEmpty), (j - 1) & 1, abort_flag, p, 31);
+      if (!ok) break;
+      tc_fence_after();
+      const float basef = (float)run;
+      float local = 0.f;
+      const bool diag = (j == 0);
+#pragma unroll 1
+      for (int ch = 3; ch >= 0; --ch) {
+        uint32_t v[32];
+        tmem_ld32(tS[j & 1] + lane_off + ch * 32, v);
+        tmem_wait_ld();
+        if (ch == 0) {            // the whole row of S is in registers or consumed: the buffer may be overwritten
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarSEmpty + (j & 1)));
+        }
+        float pr[32];
+#pragma unroll
+        for (int i = 31; i >= 0; --i) {
+          const float x = __uint_as_float(v[i]) * scale2;
+          const float e = ex2(x);
+          float sp = x > 24.f ? x : lg2(1.f + e);
+          const int col = ch * 32 + i;
+          bool allowed = true;
+          if (diag) {
+            allowed = ac ? (col <= r) : (col < r);
+            sp = allowed ? sp : 0.f;
+          }
+          local += sp;
+          const float t = basef + local;
+          float pv = ex2(fmaf(__uint_as_float(v[i]), scale2, -t));
+          if (diag) pv = allowed ? pv : 0.f;
+          pr[i] = pv;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack2<kFp16>(pr[g * 8 + 0], pr[g * 8 + 1]);
+          w.y = pack2<kFp16>(pr[g * 8 + 2], pr[g * 8 + 3]);
+          w.z = pack2<kFp16>(pr[g * 8 + 4], pr[g * 8 + 5]);
+          w.w = pack2<kFp16>(pr[g * 8 + 6], pr[g * 8 + 7]);
+          *reinterpret_cast<uint4 *>(gP + sw128_chunk_offset(r, ch * 32 + g * 8)) = w;
+        }
+      }
+      run += (double)local;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarPFull));
+    }
+    // ---- epilogue: O (TMEM) -> global, rem, log_rem
+    if (ok) ok = wait_or_abort(bar(kBarOFull), 0, abort_flag, p, 32);
+    if (ok) {
+      tc_fence_after();
+      const int gi = I * kBM + r;
+      const bool valid = gi < c.len;
+      using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
+      T *orow = reinterpret_cast<T *>(p.o.ptr) + c.boff * p.o.sb + (long long)h * p.o.sh + (c.tok0 + gi) * p.o.st;
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld32(tO + lane_off + ch * 32, v);
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int x0 = ch * 32 + g * 8;
+            if (x0 < p.head_dim) {
+              uint4 w;
+              w.x = pack2<kFp16>(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+              w.y = pack2<kFp16>(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+              w.z = pack2<kFp16>(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+              w.w = pack2<kFp16>(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+              *reinterpret_cast<uint4 *>(orow + x0) = w;
+            }
+          }
+        }
+      }
+      if (valid) {
+        const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + gi;
+        reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(ex2(-(float)run));
+        p.log_rem[idx] = -run;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) return (EncodeTiledFn) nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// 4-D map (head_dim, tokens, heads, batch) with a [64 x 128 x 1 x 1] box and the 128-byte swizzle.
+static cudaError_t make_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return cudaErrorNotSupported;
+  const cuuint64_t esz = 2;
+  long long sb_el = t.sb > 0 ? t.sb : (t.sh > 0 ? t.sh * p.heads : (long long)p.tokens * p.head_dim);
+  long long sh_el = t.sh > 0 ? t.sh : (long long)p.tokens * p.head_dim;
+  cuuint64_t dims[4] = {(cuuint64_t)p.head_dim, (cuuint64_t)p.tokens, (cuuint64_t)p.heads, (cuuint64_t)p.batch};
+  cuuint64_t strides[3] = {(cuuint64_t)t.st * esz, (cuuint64_t)sh_el * esz, (cuuint64_t)sb_el * esz};
+  cuuint32_t box[4] = {64, (cuuint32_t)kBM, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == SB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool tc_supported(int dtype, int head_dim, bool backward) {
+  if (backward) return false;
+  return (dtype == SB_DTYPE_BF16 || dtype == SB_DTYPE_F16) && head_dim % 8 == 0 && head_dim <= 128;
+}
+
+template <int D, bool kFp16>
+static cudaError_t launch_fwd_t(const KParams &p, int dtype, cudaStream_t s) {
+  CUtensorMap mq, mk, mv;
+  cudaError_t e;
+  if ((e = make_map(&mq, p.q, p, dtype)) != cudaSuccess) return e;
+  if ((e = make_map(&mk, p.k, p, dtype)) != cudaSuccess) return e;
+  if ((e = make_map(&mv, p.v, p, dtype)) != cudaSuccess) return e;
+  auto kernel = tc_fwd_kernel<D, kFp16>;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D>::kSmem);
+  if (e != cudaSuccess) return e;
+  dim3 grid(p.tiles_cap, p.head_cnt);
+  kernel<<<grid, kFwdThreads, FwdCfg<D>::kSmem, s>>>(mq, mk, mv, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches) {
+  *launches += 1;
+  const bool f16 = dtype == SB_DTYPE_F16;
+  if (p.head_dim <= 64) return f16 ? launch_fwd_t<64, true>(p, dtype, s) : launch_fwd_t<64, false>(p, dtype, s);
+  return f16 ? launch_fwd_t<128, true>(p, dtype, s) : launch_fwd_t<128, false>(p, dtype, s);
+}
+
 cudaError_t launch_tc_bwd(const KParams &, int, cudaStream_t, int *) { return cudaErrorNotSupported; }
+
 }  // namespace sb
