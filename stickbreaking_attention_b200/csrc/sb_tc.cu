@@ -1,7 +1,7 @@
-// Tensor-core kernels for bf16 / fp16 tensors: tcgen05 MMAs with TMEM accumulators, K/V tiles staged by TMA.
+// Tensor-core forward kernel for bf16 / fp16 tensors: tcgen05 MMAs with TMEM accumulators, K/V tiles staged by TMA.
 //
-// Forward (reference counterpart: _forward_one_row, sb_varlen_fwd.py:81-215).  One CTA owns a 128-row query
-// tile of one (sequence, head) and walks the key tiles from the diagonal back to the sequence start:
+// Reference counterpart: _forward_one_row, sb_varlen_fwd.py:81-215.  One CTA owns a 128-row query tile of one
+// (sequence, head) and walks the key tiles from the diagonal back to the sequence start:
 //   warp 4    TMA producer: Q once, then K and V tiles into a ring of shared-memory stages
 //   warp 5    MMA issuer:   S = Q K^T into one of two TMEM buffers, O += P V into a third
 //   warps 0-3 one thread per query row: reads its row of S from TMEM (32 columns at a time, last column
@@ -9,21 +9,9 @@
 //             registers, writes P as bf16 into the swizzled shared-memory layout the MMA reads
 // Every wait on an mbarrier is bounded; a wait that gives up records SB_DEV_WAIT_TIMEOUT and all roles
 // leave through the common exit, which frees the tensor memory.
-#include <cuda.h>
-
-#include <type_traits>
-
-#include "sb_common.cuh"
-#include "sb_ptx.cuh"
+#include "sb_tc_common.cuh"
 
 namespace sb {
-
-using namespace ptx;
-
-constexpr int kBM = kTcTile;  // 128 query rows per CTA, 128 keys per tile
-constexpr int kFwdThreads = 192;
-constexpr uint32_t kTmemCols = 512;
-constexpr int kBoxBytes = kBM * 64 * 2;  // one TMA box: 128 rows x 64 16-bit elements, 128-byte swizzled
 
 template <int D>
 struct FwdCfg {
@@ -38,39 +26,8 @@ struct FwdCfg {
 enum { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 5, kBarSFull = 9, kBarSEmpty = 11, kBarPFull = 13, kBarPEmpty = 14,
        kBarOFull = 15, kNumBars = 16 };
 
-struct Ctl {  // lives behind the barriers in shared memory
-  uint32_t tmem_base;
-  int abort;
-};
-
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag, const KParams &p,
-                                              int which) {
-  if (mbar_wait(bar, parity)) return true;
-  *abort_flag = 1;
-  if (p.status != nullptr) { p.status[0] = SB_DEV_WAIT_TIMEOUT; p.status[1] = which; }
-  return false;
-}
-
-template <bool kFp16>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if constexpr (kFp16) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-  } else {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-  }
-}
-
-// Byte offset of the 16-byte chunk holding columns [c0, c0+8) of row r in a [128 x 128] 16-bit tile stored as
-// two [128 x 64] K-major blocks with the 128-byte swizzle (chunk index XOR row mod 8).
-__device__ __forceinline__ uint32_t sw128_chunk_offset(int r, int c0) {
-  const int kb = c0 >> 6, chunk = (c0 & 63) >> 3;
-  return kb * kBoxBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
-}
-
 template <int D, bool kFp16>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const KParams p) {
   using Cfg = FwdCfg<D>;
@@ -145,13 +102,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       constexpr uint32_t idesc_s = idesc_f16(kBM, kBM, kFp16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(kBM, D, kFp16, false, true);
       auto issue_s = [&](int j) {  // S[j & 1] = Q K_j^T
-        const uint32_t kaddr = sK + (j % NS) * Cfg::kTileBytes;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-          mma_f16_ss(tS[j & 1], smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(kaddr + off, 16, 1024), idesc_s,
-                     k > 0);
-        }
+        mma_kmajor_kmajor<D>(tS[j & 1], sQ, sK + (j % NS) * Cfg::kTileBytes, idesc_s, false);
         mma_commit(bar(kBarSFull + (j & 1)));
       };
       bool ok = wait_or_abort(bar(kBarQ), 0, abort_flag, p, 20) && wait_or_abort(bar(kBarKvFull), 0, abort_flag, p, 21);
@@ -171,13 +122,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = wait_or_abort(bar(kBarPFull), j & 1, abort_flag, p, 24);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t vaddr = sV + (j % NS) * Cfg::kTileBytes;
-#pragma unroll
-        for (int ks = 0; ks < kBM / 16; ++ks) {   // 16 keys per MMA
-          const uint32_t aoff = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-          mma_f16_ss(tO, smem_desc_sw128(sP + aoff, 16, 1024), smem_desc_sw128(vaddr + ks * 2048, kBoxBytes, 1024),
-                     idesc_pv, (j > 0 || ks > 0));
-        }
+        mma_kmajor_mnmajor(tO, sP, sV + (j % NS) * Cfg::kTileBytes, idesc_pv, j > 0);   // O += P V_j
         mma_commit(bar(kBarKvEmpty + j % NS));
         mma_commit(bar(kBarPEmpty));
       }
@@ -227,15 +172,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (diag) pv = allowed ? pv : 0.f;
           pr[i] = pv;
         }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w;
-          w.x = pack2<kFp16>(pr[g * 8 + 0], pr[g * 8 + 1]);
-          w.y = pack2<kFp16>(pr[g * 8 + 2], pr[g * 8 + 3]);
-          w.z = pack2<kFp16>(pr[g * 8 + 4], pr[g * 8 + 5]);
-          w.w = pack2<kFp16>(pr[g * 8 + 6], pr[g * 8 + 7]);
-          *reinterpret_cast<uint4 *>(gP + sw128_chunk_offset(r, ch * 32 + g * 8)) = w;
-        }
+        store_row_chunk<kFp16>(gP, r, ch * 32, pr);
       }
       run += (double)local;
       fence_proxy_async_smem();
@@ -250,26 +187,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const bool valid = gi < c.len;
       using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
       T *orow = reinterpret_cast<T *>(p.o.ptr) + c.boff * p.o.sb + (long long)h * p.o.sh + (c.tok0 + gi) * p.o.st;
-#pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(tO + lane_off + ch * 32, v);
-        tmem_wait_ld();
-        if (valid) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int x0 = ch * 32 + g * 8;
-            if (x0 < p.head_dim) {
-              uint4 w;
-              w.x = pack2<kFp16>(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-              w.y = pack2<kFp16>(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-              w.z = pack2<kFp16>(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-              w.w = pack2<kFp16>(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-              *reinterpret_cast<uint4 *>(orow + x0) = w;
-            }
-          }
-        }
-      }
+      store_acc_rows<D, kFp16, T>(tO + lane_off, orow, valid, p.head_dim, 1.f);
       if (valid) {
         const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + gi;
         reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(ex2(-(float)run));
@@ -300,8 +218,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 4-D map (head_dim, tokens, heads, batch) with a [64 x 128 x 1 x 1] box and the 128-byte swizzle.
-static cudaError_t make_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype) {
+cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return cudaErrorNotSupported;
   const cuuint64_t esz = 2;
@@ -318,7 +235,7 @@ static cudaError_t make_map(CUtensorMap *map, const TensorRef &t, const KParams 
 }
 
 bool tc_supported(int dtype, int head_dim, bool backward) {
-  if (backward) return false;
+  (void)backward;
   return (dtype == SB_DTYPE_BF16 || dtype == SB_DTYPE_F16) && head_dim % 8 == 0 && head_dim <= 128;
 }
 
@@ -326,14 +243,14 @@ template <int D, bool kFp16>
 static cudaError_t launch_fwd_t(const KParams &p, int dtype, cudaStream_t s) {
   CUtensorMap mq, mk, mv;
   cudaError_t e;
-  if ((e = make_map(&mq, p.q, p, dtype)) != cudaSuccess) return e;
-  if ((e = make_map(&mk, p.k, p, dtype)) != cudaSuccess) return e;
-  if ((e = make_map(&mv, p.v, p, dtype)) != cudaSuccess) return e;
+  if ((e = make_tile_map(&mq, p.q, p, dtype)) != cudaSuccess) return e;
+  if ((e = make_tile_map(&mk, p.k, p, dtype)) != cudaSuccess) return e;
+  if ((e = make_tile_map(&mv, p.v, p, dtype)) != cudaSuccess) return e;
   auto kernel = tc_fwd_kernel<D, kFp16>;
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D>::kSmem);
   if (e != cudaSuccess) return e;
   dim3 grid(p.tiles_cap, p.head_cnt);
-  kernel<<<grid, kFwdThreads, FwdCfg<D>::kSmem, s>>>(mq, mk, mv, p);
+  kernel<<<grid, kTcThreads, FwdCfg<D>::kSmem, s>>>(mq, mk, mv, p);
   return cudaGetLastError();
 }
 
@@ -343,7 +260,5 @@ cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *laun
   if (p.head_dim <= 64) return f16 ? launch_fwd_t<64, true>(p, dtype, s) : launch_fwd_t<64, false>(p, dtype, s);
   return f16 ? launch_fwd_t<128, true>(p, dtype, s) : launch_fwd_t<128, false>(p, dtype, s);
 }
-
-cudaError_t launch_tc_bwd(const KParams &, int, cudaStream_t, int *) { return cudaErrorNotSupported; }
 
 }  // namespace sb

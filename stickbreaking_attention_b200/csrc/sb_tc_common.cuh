@@ -1,0 +1,125 @@
+// Pieces shared by the tensor-core forward and backward kernels.
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "sb_common.cuh"
+#include "sb_ptx.cuh"
+
+namespace sb {
+
+using namespace ptx;
+
+constexpr int kBM = kTcTile;  // 128 query rows per CTA, 128 keys per tile
+constexpr int kTcThreads = 192;  // warps 0-3: one thread per tile row; warp 4: TMA; warp 5: MMA issue
+constexpr uint32_t kTmemCols = 512;
+constexpr int kBoxBytes = kBM * 64 * 2;  // one TMA box: 128 rows x 64 16-bit elements, 128-byte swizzled
+
+struct Ctl {  // lives behind the barriers in shared memory
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag, const KParams &p,
+                                              int which) {
+  if (mbar_wait(bar, parity)) return true;
+  *abort_flag = 1;
+  if (p.status != nullptr) { p.status[0] = SB_DEV_WAIT_TIMEOUT; p.status[1] = which; }
+  return false;
+}
+
+template <bool kFp16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kFp16) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+}
+
+// Byte offset of the 16-byte chunk holding columns [c0, c0+8) of row r in a [128 x 128] 16-bit tile stored as
+// two [128 x 64] blocks of 128-byte rows with the 128-byte swizzle (chunk index XOR row mod 8).  Read by the
+// MMA either as a K-major operand (rows = M, columns = K) or as an MN-major one (rows = K, columns = M).
+__device__ __forceinline__ uint32_t sw128_chunk_offset(int r, int c0) {
+  const int kb = c0 >> 6, chunk = (c0 & 63) >> 3;
+  return kb * kBoxBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
+}
+
+// Stores 32 consecutive columns (first column c0, a multiple of 32) of row r of such a tile.
+template <bool kFp16>
+__device__ __forceinline__ void store_row_chunk(uint8_t *tile, int r, int c0, const float (&x)[32]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint4 w;
+    w.x = pack2<kFp16>(x[g * 8 + 0], x[g * 8 + 1]);
+    w.y = pack2<kFp16>(x[g * 8 + 2], x[g * 8 + 3]);
+    w.z = pack2<kFp16>(x[g * 8 + 4], x[g * 8 + 5]);
+    w.w = pack2<kFp16>(x[g * 8 + 6], x[g * 8 + 7]);
+    *reinterpret_cast<uint4 *>(tile + sw128_chunk_offset(r, c0 + g * 8)) = w;
+  }
+}
+
+// TMEM accumulator rows (one per thread) -> 16-bit global rows, `mul` applied, columns >= head_dim dropped.
+template <int D, bool kFp16, typename T>
+__device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool valid, int head_dim, float mul) {
+#pragma unroll 1
+  for (int ch = 0; ch < D / 32; ++ch) {
+    uint32_t v[32];
+    tmem_ld32(tmem_addr + ch * 32, v);
+    tmem_wait_ld();
+    if (valid) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int x0 = ch * 32 + g * 8;
+        if (x0 < head_dim) {
+          uint4 w;
+          w.x = pack2<kFp16>(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
+          w.y = pack2<kFp16>(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
+          w.z = pack2<kFp16>(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
+          w.w = pack2<kFp16>(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
+          *reinterpret_cast<uint4 *>(grow + x0) = w;
+        }
+      }
+    }
+  }
+}
+
+// MMA issue helpers (called by one thread).  A K-major [128 x 16*n] operand advances 32 bytes per 16-element
+// K step inside a 64-element block and one box per block; an MN-major one advances 16 rows (2048 bytes).
+template <int KDIM>
+__device__ __forceinline__ void mma_kmajor_kmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
+                                                  bool accumulate) {
+#pragma unroll
+  for (int k = 0; k < KDIM / 16; ++k) {
+    const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
+    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + off, 16, 1024), smem_desc_sw128(b_addr + off, 16, 1024), idesc,
+               accumulate || k > 0);
+  }
+}
+// A: K-major [128 x 128];  B: rows = K (128), columns = N, MN-major.
+__device__ __forceinline__ void mma_kmajor_mnmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
+                                                   bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < kBM / 16; ++ks) {
+    const uint32_t aoff = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + aoff, 16, 1024), smem_desc_sw128(b_addr + ks * 2048, kBoxBytes, 1024),
+               idesc, accumulate || ks > 0);
+  }
+}
+// A and B both stored with rows = K (128): A^T B.
+__device__ __forceinline__ void mma_mnmajor_mnmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
+                                                    bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < kBM / 16; ++ks)
+    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + ks * 2048, kBoxBytes, 1024),
+               smem_desc_sw128(b_addr + ks * 2048, kBoxBytes, 1024), idesc, accumulate || ks > 0);
+}
+
+// host: 4-D TMA map (head_dim, tokens, heads, batch), [64 x 128 x 1 x 1] box, 128-byte swizzle, zero fill
+cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype);
+
+}  // namespace sb
