@@ -123,6 +123,29 @@ SB_EXPORT int sb_fwd(const SbParams *p, void *stream);
  * ops ::varlen_bwd (sb_varlen_bwd.py:542-641) and ::attn_bwd (sb_attn/sb_bwd.py:208-297). */
 SB_EXPORT int sb_bwd(const SbParams *p, void *stream);
 
+/* Forward pass for callers that cannot allocate device memory.  No counterpart in the reference, which
+ * allocates freely inside its launchers.
+ *
+ * Who needs it: a host that hands an operator a fixed memory arena at start-up and forbids later allocation
+ * (inference servers, embedded runtimes); a latency-critical loop in which cudaMalloc's implicit device-wide
+ * synchronisation is unacceptable; a plain C caller that only holds the tensors it was given and has no
+ * allocator to ask.  Such a caller still passes q, k, v, o, rem and log_rem, but leaves `workspace` and
+ * `workspace_bytes` unset: the forward's scratch (the sequence table built from cu_seqlens) lives in an array
+ * of SB_STATIC_SCRATCH_BYTES bytes inside the library's device image.  Every GPU that loads the library holds
+ * that array until the process exits.
+ *
+ * Same results as sb_fwd.  Calls that need more scratch than the array holds (sb_workspace_bytes(p, 0) >
+ * SB_STATIC_SCRATCH_BYTES, i.e. beyond about 5400 packed sequences; a fixed-length batch always fits) return
+ * SB_ERR_WORKSPACE with a message and launch nothing.  The function calls no cudaMalloc, cudaFree or any
+ * other allocating routine.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before any stream capture begins.  All calls on a device share the one
+ * array, which keeps whatever the previous call left in it; each call rewrites the parts it reads.  Two calls
+ * whose kernels may overlap on the GPU (different streams, or different threads) race on it: serialise them. */
+#define SB_STATIC_SCRATCH_BYTES 65536
+SB_EXPORT int sb_fwd_static_scratch(const SbParams *p, void *stream);
+
 /* Which kernels sb_fwd / sb_bwd run for these parameters (an SbKernelPath), or -1 if invalid. */
 SB_EXPORT int sb_kernel_path(const SbParams *p);
 

@@ -15,13 +15,14 @@ LIB_PATH = os.path.join(_PKG_DIR, "libsb_b200.so")
 
 SB_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 SB_PATH_SIMT, SB_PATH_TCGEN05 = 0, 1
+SB_STATIC_SCRATCH_BYTES = 65536
 SB_FLAG_FORCE_SIMT, SB_FLAG_CHECK_LEADING_ZERO, SB_FLAG_BWD_SKIP_DKV, SB_FLAG_BWD_SKIP_DQ = 1, 2, 4, 8
 SB_DEV_MESSAGES = {
     1: "cu_seqlens is invalid (not non-decreasing, beyond the token count, longer than max_seqlens, "
        "or without its leading zero); offending sequence index: {0}",
     2: "a bounded on-chip wait timed out in barrier {0}",
 }
-EXPORTS = ("sb_workspace_bytes", "sb_fwd", "sb_bwd", "sb_kernel_path", "sb_last_launch_count",
+EXPORTS = ("sb_workspace_bytes", "sb_fwd", "sb_bwd", "sb_fwd_static_scratch", "sb_kernel_path", "sb_last_launch_count",
            "sb_last_error", "sb_abi_version")
 
 
@@ -64,7 +65,7 @@ def load(path: str | None = None) -> ctypes.CDLL:
     lib = ctypes.CDLL(path)
     lib.sb_workspace_bytes.restype = ctypes.c_size_t
     lib.sb_workspace_bytes.argtypes = [ctypes.POINTER(SbParams), ctypes.c_int]
-    for name in ("sb_fwd", "sb_bwd"):
+    for name in ("sb_fwd", "sb_bwd", "sb_fwd_static_scratch"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(SbParams), ctypes.c_void_p]

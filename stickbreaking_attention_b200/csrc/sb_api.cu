@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "sb_common.cuh"
 
@@ -201,6 +202,50 @@ static int run(const SbParams *p, void *stream, bool backward) {
   return SB_OK;
 }
 
+// ---- built-in scratch for callers that cannot allocate ---------------------------------------------
+// One array per device that loads the library, resident until the process exits.  Host code may not use
+// the symbol as an address: the device address is looked up once per device and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[SB_STATIC_SCRATCH_BYTES];
+static std::mutex g_static_scratch_mu;
+static void *g_static_scratch_ptr[64];
+
+static int static_scratch_address(void **out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(SB_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(SB_ERR_CUDA, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> guard(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void *ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);   // resolves for the current device
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(SB_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch): %s", cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return SB_OK;
+}
+
+static int run_fwd_static_scratch(const SbParams *p, void *stream) {
+  g_err[0] = 0;
+  g_launches = 0;
+  Plan pl;
+  int rc = make_plan(p, pl, false);
+  if (rc) return rc;
+  if (pl.total_fwd > (size_t)SB_STATIC_SCRATCH_BYTES)
+    return fail(SB_ERR_WORKSPACE,
+                "sb_fwd_static_scratch: this call needs %zu bytes of scratch but the built-in scratch holds %d "
+                "(about 5400 packed sequences); use sb_fwd with a caller-provided workspace",
+                pl.total_fwd, (int)SB_STATIC_SCRATCH_BYTES);
+  if ((rc = device_ok())) return rc;
+  void *scratch = nullptr;
+  if ((rc = static_scratch_address(&scratch))) return rc;
+  SbParams with_scratch = *p;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = SB_STATIC_SCRATCH_BYTES;
+  return run(&with_scratch, stream, false);
+}
+
 }  // namespace sb
 
 extern "C" {
@@ -224,6 +269,8 @@ int sb_kernel_path(const SbParams *p) {
 int sb_last_launch_count(void) { return sb::g_launches; }
 
 const char *sb_last_error(void) { return sb::g_err; }
+
+int sb_fwd_static_scratch(const SbParams *p, void *stream) { return sb::run_fwd_static_scratch(p, stream); }
 
 int sb_abi_version(void) { return SB_ABI_VERSION; }
 
