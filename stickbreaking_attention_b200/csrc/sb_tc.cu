@@ -26,6 +26,42 @@ struct FwdCfg {
 enum { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 5, kBarSFull = 9, kBarSEmpty = 11, kBarPFull = 13, kBarPEmpty = 14,
        kBarOFull = 15, kNumBars = 16 };
 
+// One row, 32 consecutive key columns starting at c0, visited from the last column to the first.
+//   x = z log2(e), clamped at 30 (sigmoid is 1 to 1e-9 there);  e = 2^x;  1 - beta = 1 / (1 + e)
+//   p = beta * R with R the product of (1 - beta) over the later keys (kept in registers, may underflow to 0,
+//   which is also what p rounds to then);  R *= (1 - beta)
+// The tile's contribution to log2 of the product is kept exactly enough for 131072-token rows by taking
+// log2 of the product of four (1 + e) at a time: 2.25 transcendentals per score instead of 3.
+template <bool kFp16, bool kDiag>
+__device__ __forceinline__ void fwd_row_chunk(const uint32_t (&v)[32], int c0, int r, int ac, float scale2, float &R,
+                                              float &logsum, uint8_t *tile_p) {
+  float pr[32];
+  float prod = 1.f;
+#pragma unroll
+  for (int i = 31; i >= 0; --i) {
+    const float x = fminf(__uint_as_float(v[i]) * scale2, 30.f);
+    const float e = ex2(x);
+    float t1 = 1.f + e;
+    float rinv = rcp(t1);
+    float pv = (e * rinv) * R;
+    if (kDiag) {
+      const int col = c0 + i;
+      const bool allowed = ac ? (col <= r) : (col < r);
+      pv = allowed ? pv : 0.f;
+      rinv = allowed ? rinv : 1.f;
+      t1 = allowed ? t1 : 1.f;
+    }
+    R *= rinv;
+    prod *= t1;
+    if ((i & 3) == 0) {
+      logsum += lg2(prod);
+      prod = 1.f;
+    }
+    pr[i] = pv;
+  }
+  store_row_chunk<kFp16>(tile_p, r, c0, pr);
+}
+
 template <int D, bool kFp16>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -141,40 +177,43 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok && j > 0) ok = wait_or_abort(bar(kBarPEmpty), (j - 1) & 1, abort_flag, p, 31);
       if (!ok) break;
       tc_fence_after();
-      const float basef = (float)run;
-      float local = 0.f;
-      const bool diag = (j == 0);
+      const uint32_t ts = tS[j & 1] + lane_off;
+      float R = ex2(-(float)run);   // product of (1 - beta) over the keys after this tile
+      float logsum = 0.f;           // sum of log2(1 + 2^x) over this tile's allowed keys
+      if (j == 0) {                 // diagonal tile: masked, one rolled loop
 #pragma unroll 1
-      for (int ch = 3; ch >= 0; --ch) {
-        uint32_t v[32];
-        tmem_ld32(tS[j & 1] + lane_off + ch * 32, v);
-        tmem_wait_ld();
-        if (ch == 0) {            // the whole row of S is in registers or consumed: the buffer may be overwritten
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(kBarSEmpty + (j & 1)));
-        }
-        float pr[32];
-#pragma unroll
-        for (int i = 31; i >= 0; --i) {
-          const float x = __uint_as_float(v[i]) * scale2;
-          const float e = ex2(x);
-          float sp = x > 24.f ? x : lg2(1.f + e);
-          const int col = ch * 32 + i;
-          bool allowed = true;
-          if (diag) {
-            allowed = ac ? (col <= r) : (col < r);
-            sp = allowed ? sp : 0.f;
+        for (int ch = 3; ch >= 0; --ch) {
+          uint32_t v[32];
+          tmem_ld32(ts + ch * 32, v);
+          tmem_wait_ld_regs(v);
+          if (ch == 0) {            // the whole row of S is in registers or consumed: the buffer may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarSEmpty + (j & 1)));
           }
-          local += sp;
-          const float t = basef + local;
-          float pv = ex2(fmaf(__uint_as_float(v[i]), scale2, -t));
-          if (diag) pv = allowed ? pv : 0.f;
-          pr[i] = pv;
+          fwd_row_chunk<kFp16, true>(v, ch * 32, r, ac, scale2, R, logsum, gP);
         }
-        store_row_chunk<kFp16>(gP, r, ch * 32, pr);
+      } else {                      // the row is read 32 columns at a time, one load ahead of the arithmetic
+        uint32_t va[32], vb[32];
+        tmem_ld32(ts + 96, va);
+#pragma unroll 1
+        for (int pair = 1; pair >= 0; --pair) {
+          const int c0 = pair * 64;
+          tmem_wait_ld_regs(va);
+          tmem_ld32(ts + c0, vb);
+          fwd_row_chunk<kFp16, false>(va, c0 + 32, r, ac, scale2, R, logsum, gP);
+          tmem_wait_ld_regs(vb);
+          if (pair == 1) {
+            tmem_ld32(ts + 32, va);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarSEmpty + (j & 1)));
+          }
+          fwd_row_chunk<kFp16, false>(vb, c0, r, ac, scale2, R, logsum, gP);
+        }
       }
-      run += (double)local;
+      run += (double)logsum;
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPFull));

@@ -15,40 +15,113 @@
 namespace sb {
 
 // One row, 32 consecutive key columns starting at c0.  s: raw q.k accumulators, dp: <dO_i, v_j>.
-//   x = z log2(e);  sp = log2(1 + 2^x);  A = 2^(x + r1 + sum of sp over the columns before this one)
-//   G = A (dP - dR);  C = gpre + inclusive prefix of G;  beta = 1 - 1/(1 + 2^x);  dz = G - beta C
-// `masked` tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
-template <bool kFp16, bool kStoreA>
-__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], int c0, int r,
-                                              bool masked, bool diag, int ac, bool row_valid, float scale2, float r1,
-                                              float gpre, float dr, float &spl, float &gs, uint8_t *tile_a,
-                                              uint8_t *tile_z) {
-  float pa[32], pz[32];
+//   x = z log2(e), clamped at 30;  e = 2^x;  1 - beta = 1 / (1 + e);  beta = e / (1 + e)
+//   A_j = beta_j * W_j,  W_j = product of (1 - beta) over the allowed keys after j up to the diagonal
+//   G = A (dP - dR);  C = gpre + inclusive prefix of G;  dz = G - beta C
+// Three sweeps over the 32 columns, all in registers: (1) e and 1/(1+e), and log2 of the product of (1 + e) four
+// factors at a time, which gives the log-space sum through the end of the chunk; (2) last column to first: W is
+// seeded with 2^(r1 + that sum) -- the largest value it takes in the chunk -- and shrinks by (1 - beta) per
+// column, so it only underflows where A rounds to zero anyway; (3) first column to last: the prefix sum of G and
+// dz.  2.3 transcendentals per score (ex2, rcp, lg2 / 4, ex2 / 32).
+// kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
+template <bool kFp16, bool kStoreA, bool kMasked>
+__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], int c0, int r, bool diag,
+                                              int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
+                                              float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+  float be[32], ri[32];
+  float prod = 1.f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    const float sv = __uint_as_float(s[i]);
-    const float x = sv * scale2;
-    const float t1 = 1.f + ex2(x);
-    float sp = x > 24.f ? x : lg2(t1);
-    float a = ex2(fmaf(sv, scale2, r1 + spl));
-    bool allowed = true;
-    if (masked) {
+    const float x = fminf(__uint_as_float(s[i]) * scale2, 30.f);
+    float e = ex2(x);
+    float t1 = 1.f + e;
+    float rinv = rcp(t1);
+    if (kMasked) {
       const int col = c0 + i;
-      allowed = row_valid && (!diag || (ac ? col <= r : col < r));
-      sp = allowed ? sp : 0.f;
-      a = allowed ? a : 0.f;
+      const bool allowed = row_valid && (!diag || (ac ? col <= r : col < r));
+      e = allowed ? e : 0.f;
+      t1 = allowed ? t1 : 1.f;
+      rinv = allowed ? rinv : 1.f;
     }
-    spl += sp;
-    const float g = a * (__uint_as_float(dp[i]) - dr);
+    be[i] = e * rinv;
+    ri[i] = rinv;
+    prod *= t1;
+    if ((i & 3) == 3) {
+      logsum += lg2(prod);
+      prod = 1.f;
+    }
+  }
+  float W = ex2(r1 + logsum);
+  float pa[32];
+#pragma unroll
+  for (int i = 31; i >= 0; --i) {
+    pa[i] = be[i] * W;
+    W *= ri[i];
+  }
+  float pz[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float g = pa[i] * (__uint_as_float(dp[i]) - dr);
+    if (kMasked) {   // rows past the sequence end carry arbitrary values: select, do not rely on 0 * x
+      const int col = c0 + i;
+      const bool allowed = row_valid && (!diag || (ac ? col <= r : col < r));
+      g = allowed ? g : 0.f;
+      pa[i] = allowed ? pa[i] : 0.f;
+    }
     gs += g;
-    const float beta = 1.f - rcp(t1);
-    float dz = fmaf(-beta, gpre + gs, g);
-    if (masked) dz = allowed ? dz : 0.f;
-    pa[i] = a;
-    pz[i] = dz;
+    pz[i] = fmaf(-be[i], gpre + gs, g);
+    if (kMasked) pz[i] = row_valid ? pz[i] : 0.f;
   }
   if constexpr (kStoreA) store_row_chunk<kFp16>(tile_a, r, c0, pa);
   store_row_chunk<kFp16>(tile_z, r, c0, pz);
+}
+
+// One row of a 128-key tile.  `empty_bar` is signalled (one arrival per warp) as soon as the last columns of S and
+// dP are in registers.  The plain version reads TMEM one 32-column load ahead of the arithmetic.
+template <bool kFp16, bool kStoreA>
+__device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r, float scale2,
+                                             float r1, float gpre, float dr, float &gs, float &logsum, uint8_t *tile_a,
+                                             uint8_t *tile_z) {
+  uint32_t s0[32], d0[32], s1[32], d1[32];
+  tmem_ld32(ts, s0);
+  tmem_ld32(tp, d0);
+#pragma unroll 1
+  for (int pair = 0; pair < 2; ++pair) {
+    const int c0 = pair * 64;
+    tmem_wait_ld_regs(s0, d0);
+    tmem_ld32(ts + c0 + 32, s1);
+    tmem_ld32(tp + c0 + 32, d1);
+    bwd_row_chunk<kFp16, kStoreA, false>(s0, d0, c0, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    tmem_wait_ld_regs(s1, d1);
+    if (pair == 0) {
+      tmem_ld32(ts + 64, s0);
+      tmem_ld32(tp + 64, d0);
+    } else {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar);
+    }
+    bwd_row_chunk<kFp16, kStoreA, false>(s1, d1, c0 + 32, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+  }
+}
+
+template <bool kFp16, bool kStoreA>
+__device__ __forceinline__ void bwd_row_pass_masked(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r,
+                                                    bool diag, int ac, bool row_valid, float scale2, float r1, float gpre,
+                                                    float dr, float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+#pragma unroll 1
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t s0[32], d0[32];
+    tmem_ld32(ts + ch * 32, s0);
+    tmem_ld32(tp + ch * 32, d0);
+    tmem_wait_ld_regs(s0, d0);
+    if (ch == 3) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar);
+    }
+    bwd_row_chunk<kFp16, kStoreA, true>(s0, d0, ch * 32, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+  }
 }
 
 // =======================================================================================================
@@ -188,23 +261,14 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float r1f = (float)r1;
       p.bnd_r1[slot0 + (long long)j * kBM] = r1f;
       p.bnd_s2[slot0 + (long long)j * kBM] = gpre;
-      float spl = 0.f, gs = 0.f;
-      const bool diag = (j == I);
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tS + lane_off + ch * 32, s);
-        tmem_ld32(tP + lane_off + ch * 32, dp);
-        tmem_wait_ld();
-        if (ch == 3) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(qSpEmpty));
-        }
-        bwd_row_chunk<kFp16, false>(s, dp, ch * 32, r, diag, diag, p.attend_current, true, scale2, r1f, gpre, dr, spl,
-                                    gs, nullptr, gZ);
-      }
-      r1 += (double)spl;
+      float gs = 0.f, logsum = 0.f;
+      if (j == I)
+        bwd_row_pass_masked<kFp16, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, true, p.attend_current, true,
+                                          scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ);
+      else
+        bwd_row_pass<kFp16, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, scale2, r1f, gpre, dr, gs, logsum,
+                                   nullptr, gZ);
+      r1 += (double)logsum;
       gpre += gs;
       fence_proxy_async_smem();
       __syncwarp();
@@ -368,23 +432,14 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (ok && i > 0) ok = wait_or_abort(bar(vAzEmpty), (i - 1) & 1, abort_flag, p, 231);
       if (!ok) break;
       tc_fence_after();
-      float spl = 0.f, gs = 0.f;
+      float gs = 0.f, logsum = 0.f;
       const bool diag = (i == 0);
-      const bool masked = diag || (I == c.n_tiles - 1);
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tS + lane_off + ch * 32, s);
-        tmem_ld32(tP + lane_off + ch * 32, dp);
-        tmem_wait_ld();
-        if (ch == 3) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(vSpEmpty));
-        }
-        bwd_row_chunk<kFp16, true>(s, dp, ch * 32, r, masked, diag, p.attend_current, valid, scale2, r1f, gpre, dr,
-                                   spl, gs, gA, gZ);
-      }
+      if (diag || I == c.n_tiles - 1)
+        bwd_row_pass_masked<kFp16, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, diag, p.attend_current, valid,
+                                         scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      else
+        bwd_row_pass<kFp16, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, scale2, r1f, gpre, dr, gs, logsum,
+                                  gA, gZ);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(vAzFull));
