@@ -15,16 +15,16 @@ namespace sb {
 
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = D == 128 ? 2 : 4;
+  static constexpr int kStages = D == 128 ? 2 : 3;
   static constexpr int kTileBytes = kBM * D * 2;
   static constexpr int kPBytes = kBM * kBM * 2;
   static constexpr int kBarBytes = 256;
-  static constexpr int kSmem = 1024 + kTileBytes * (1 + 2 * kStages) + kPBytes + kBarBytes;
+  static constexpr int kSmem = 1024 + kTileBytes * (1 + 2 * kStages) + 2 * kPBytes + kBarBytes;
 };
 
 // barrier slots (8 bytes each) inside the barrier block
-enum { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 5, kBarSFull = 9, kBarSEmpty = 11, kBarPFull = 13, kBarPEmpty = 14,
-       kBarOFull = 15, kNumBars = 16 };
+enum { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 5, kBarSFull = 9, kBarSEmpty = 11, kBarPFull = 13, kBarPEmpty = 15,
+       kBarOFull = 17, kNumBars = 18 };
 
 // One row, 32 consecutive key columns starting at c0, visited from the last column to the first.
 //   x = z log2(e), clamped at 30 (sigmoid is 1 to 1e-9 there);  e = 2^x;  1 - beta = 1 / (1 + e)
@@ -80,8 +80,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t sK = sQ + Cfg::kTileBytes;
   const uint32_t sV = sK + NS * Cfg::kTileBytes;
   const uint32_t sP = sV + NS * Cfg::kTileBytes;
-  const uint32_t sBar = sP + Cfg::kPBytes;
-  uint8_t *gP = gbase + (sP - base);
+  const uint32_t sBar = sP + 2 * Cfg::kPBytes;
+  uint8_t *gP0 = gbase + (sP - base);
   Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + kNumBars * 8);
   volatile int *abort_flag = &ctl->abort;
   auto bar = [&](int i) { return sBar + 8u * i; };
@@ -96,8 +96,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(bar(kBarQ), 1);
     for (int s = 0; s < NS; ++s) { mbar_init(bar(kBarKvFull + s), 1); mbar_init(bar(kBarKvEmpty + s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(bar(kBarSFull + s), 1); mbar_init(bar(kBarSEmpty + s), 4); }
-    mbar_init(bar(kBarPFull), 4);
-    mbar_init(bar(kBarPEmpty), 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(bar(kBarPFull + s), 4); mbar_init(bar(kBarPEmpty + s), 1); }
     mbar_init(bar(kBarOFull), 1);
     ctl->abort = 0;
     fence_barrier_init();
@@ -155,12 +154,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tc_fence_after();
           issue_s(jn);
         }
-        ok = wait_or_abort(bar(kBarPFull), j & 1, abort_flag, p, 24);
+        ok = wait_or_abort(bar(kBarPFull + (j & 1)), (j >> 1) & 1, abort_flag, p, 24);
         if (!ok) break;
         tc_fence_after();
-        mma_kmajor_mnmajor(tO, sP, sV + (j % NS) * Cfg::kTileBytes, idesc_pv, j > 0);   // O += P V_j
+        mma_kmajor_mnmajor(tO, sP + (j & 1) * Cfg::kPBytes, sV + (j % NS) * Cfg::kTileBytes, idesc_pv, j > 0);   // O += P V_j
         mma_commit(bar(kBarKvEmpty + j % NS));
-        mma_commit(bar(kBarPEmpty));
+        mma_commit(bar(kBarPEmpty + (j & 1)));
       }
       if (ok) mma_commit(bar(kBarOFull));
     }
@@ -174,7 +173,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       ok = wait_or_abort(bar(kBarSFull + (j & 1)), (j >> 1) & 1, abort_flag, p, 30);
-      if (ok && j > 0) ok = wait_or_abort(bar(kBarPEmpty), (j - 1) & 1, abort_flag, p, 31);
+      if (ok && j >= 2) ok = wait_or_abort(bar(kBarPEmpty + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, p, 31);
+      uint8_t *gP = gP0 + (j & 1) * Cfg::kPBytes;
       if (!ok) break;
       tc_fence_after();
       const uint32_t ts = tS[j & 1] + lane_off;
@@ -216,7 +216,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       run += (double)logsum;
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarPFull));
+      if (lane == 0) mbar_arrive(bar(kBarPFull + (j & 1)));
     }
     // ---- epilogue: O (TMEM) -> global, rem, log_rem
     if (ok) ok = wait_or_abort(bar(kBarOFull), 0, abort_flag, p, 32);
