@@ -75,7 +75,7 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   for (const SbTensor *t : others)
     if (t->ptr != nullptr && !tma_friendly(*t, esize)) tc = false;
   pl.path = tc ? SB_PATH_TCGEN05 : SB_PATH_SIMT;
-  pl.tile = tc ? kTcTile : kSimtTile;
+  pl.tile = tc ? tc_tile(p->head_dim, backward) : kSimtTile;
   const long long T = p->tokens;
   pl.max_seqlen = (p->max_seqlen == 0 || p->max_seqlen > T) ? (int)T : p->max_seqlen;
   if (p->cu_seqlens == nullptr) pl.max_seqlen = (int)T;
@@ -97,8 +97,9 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   if (chunk < 1) chunk = 1;
   if (chunk > (size_t)p->heads) chunk = p->heads;
   pl.chunk_heads = (int)chunk;
-  pl.total_fwd = pl.off_bnd;
-  pl.total_bwd = pl.off_bnd + 2 * pl.bnd_bytes_per_head * chunk;
+  const size_t trace_bytes = (p->reserved & 0x100) ? kTraceBytes : 0;   // experiments only
+  pl.total_fwd = pl.off_bnd + trace_bytes;
+  pl.total_bwd = pl.off_bnd + 2 * pl.bnd_bytes_per_head * chunk + trace_bytes;
   return SB_OK;
 }
 
@@ -153,9 +154,12 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   k.cu64 = p->cu_seqlens_int64;
   k.batch = p->batch; k.heads = p->heads; k.head_dim = p->head_dim; k.num_seq = p->num_seq;
   k.tokens = p->tokens;
+  char *ws_end = reinterpret_cast<char *>(p->workspace) + (backward ? pl.total_bwd : pl.total_fwd);
   k.attend_current = p->attend_current ? 1 : 0;
   k.scale = p->logit_scale;
   k.check_leading_zero = (p->cu_seqlens != nullptr && (p->flags & SB_FLAG_CHECK_LEADING_ZERO)) ? 1 : 0;
+  k.dbg = p->reserved & 0xff;
+  k.trace = (p->reserved & 0x100) ? reinterpret_cast<unsigned long long *>(ws_end - kTraceBytes) : nullptr;
   k.skip_dq = (p->flags & SB_FLAG_BWD_SKIP_DQ) ? 1 : 0;
   k.skip_dkv = (p->flags & SB_FLAG_BWD_SKIP_DKV) ? 1 : 0;
   k.tile = pl.tile; k.tiles_cap = pl.tiles_cap; k.n_max = pl.n_max; k.max_seqlen = pl.max_seqlen;

@@ -38,6 +38,8 @@ struct KParams {
   int max_seqlen;
   int check_leading_zero;  // the element before cu[0] must be 0
   int skip_dq, skip_dkv;   // timing aids: leave one of the two backward kernels out
+  int dbg;                 // experiments only (SbParams.reserved): 0 = normal arithmetic
+  unsigned long long *trace;  // experiments only: event log of block (0,0) in the workspace tail, or nullptr
   // workspace views
   int *hdr;            // [0] abort flag, [1] end of the last sequence (varlen)
   int *tile_prefix;    // [num_seq + 1]  exclusive prefix of tiles per sequence (varlen)
@@ -115,6 +117,21 @@ cudaError_t launch_simt_bwd(const KParams &p, int dtype, cudaStream_t s, int *la
 cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
 cudaError_t launch_tc_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
 bool tc_supported(int dtype, int head_dim, bool backward);
+int tc_tile(int head_dim, bool backward);   // rows per work item of the tensor-core kernels
+cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s);
+
+constexpr size_t kTraceBytes = 8 * 1024 * 16;   // workspace tail reserved for the event log
+
+// Event log of block (0,0): each logging thread owns a lane of 1024 entries [tag << 32 | step][SM clock]
+// and keeps its own cursor, so that logging costs two stores and no round trip.
+__device__ __forceinline__ void trace_event(const KParams &p, int lane_id, int &cursor, unsigned tag, unsigned step) {
+  if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || cursor >= 1023) return;
+  const unsigned long long t = (unsigned long long)clock64();   // SM clock: all logging threads share one SM
+  unsigned long long *slot = p.trace + ((size_t)lane_id * 1024 + cursor) * 2;
+  slot[0] = ((unsigned long long)tag << 32) | step;
+  slot[1] = t;
+  ++cursor;
+}
 
 constexpr int kSimtTile = 32;
 constexpr int kTcTile = 128;

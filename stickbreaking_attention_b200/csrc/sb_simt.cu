@@ -75,10 +75,14 @@ __global__ void __launch_bounds__(256) prep_kernel(KParams p) {
   }
 }
 
-__global__ void clear_hdr_kernel(int *hdr) { if (threadIdx.x < 4) hdr[threadIdx.x] = 0; }
+__global__ void clear_hdr_kernel(int *hdr, unsigned long long *trace) {
+  if (threadIdx.x < 4) hdr[threadIdx.x] = 0;
+  if (trace != nullptr)
+    for (int i = threadIdx.x; i < (int)(kTraceBytes / 8); i += blockDim.x) trace[i] = 0;
+}
 
 cudaError_t launch_prep(const KParams &p, cudaStream_t s) {
-  clear_hdr_kernel<<<1, 32, 0, s>>>(p.hdr);
+  clear_hdr_kernel<<<1, 32, 0, s>>>(p.hdr, p.trace);
   if (p.cu != nullptr) prep_kernel<<<1, 256, 0, s>>>(p);
   return cudaGetLastError();
 }

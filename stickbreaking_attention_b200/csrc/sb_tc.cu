@@ -30,34 +30,37 @@ enum { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 5, kBarSFull = 9, kBarSEmpty = 1
 //   x = z log2(e), clamped at 30 (sigmoid is 1 to 1e-9 there);  e = 2^x;  1 - beta = 1 / (1 + e)
 //   p = beta * R with R the product of (1 - beta) over the later keys (kept in registers, may underflow to 0,
 //   which is also what p rounds to then);  R *= (1 - beta)
-// The tile's contribution to log2 of the product is kept exactly enough for 131072-token rows by taking
-// log2 of the product of four (1 + e) at a time: 2.25 transcendentals per score instead of 3.
+// Four columns share one reciprocal and one logarithm (of the product of their (1 + e)): 1.5 transcendentals per
+// score.  The logarithms give the tile's contribution to log2 of the product exactly enough for 131072-token rows.
 template <bool kFp16, bool kDiag>
 __device__ __forceinline__ void fwd_row_chunk(const uint32_t (&v)[32], int c0, int r, int ac, float scale2, float &R,
                                               float &logsum, uint8_t *tile_p) {
   float pr[32];
-  float prod = 1.f;
 #pragma unroll
-  for (int i = 31; i >= 0; --i) {
-    const float x = fminf(__uint_as_float(v[i]) * scale2, 30.f);
-    const float e = ex2(x);
-    float t1 = 1.f + e;
-    float rinv = rcp(t1);
-    float pv = (e * rinv) * R;
-    if (kDiag) {
-      const int col = c0 + i;
-      const bool allowed = ac ? (col <= r) : (col < r);
-      pv = allowed ? pv : 0.f;
-      rinv = allowed ? rinv : 1.f;
-      t1 = allowed ? t1 : 1.f;
+  for (int g = 7; g >= 0; --g) {   // four columns at a time, last group first
+    float e[4], t[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      e[i] = ex2(fminf(__uint_as_float(v[4 * g + i]) * scale2, 30.f));
+      t[i] = 1.f + e[i];
+      if (kDiag) {
+        const int col = c0 + 4 * g + i;
+        const bool allowed = ac ? (col <= r) : (col < r);
+        e[i] = allowed ? e[i] : 0.f;
+        t[i] = allowed ? t[i] : 1.f;
+      }
     }
-    R *= rinv;
-    prod *= t1;
-    if ((i & 3) == 0) {
-      logsum += lg2(prod);
-      prod = 1.f;
-    }
-    pr[i] = pv;
+    // one reciprocal and one logarithm for the four factors (1 + e): 1/t_i = (1 / t0 t1 t2 t3) * (product of the others)
+    const float p01 = t[0] * t[1], p23 = t[2] * t[3];
+    const float prod = p01 * p23;
+    const float rp = rcp(prod);
+    logsum += lg2(prod);
+    const float a = rp * p23, b = rp * p01;
+    const float ri3 = b * t[2], ri2 = b * t[3], ri1 = a * t[0], ri0 = a * t[1];
+    pr[4 * g + 3] = (e[3] * ri3) * R; R *= ri3;
+    pr[4 * g + 2] = (e[2] * ri2) * R; R *= ri2;
+    pr[4 * g + 1] = (e[1] * ri1) * R; R *= ri1;
+    pr[4 * g + 0] = (e[0] * ri0) * R; R *= ri0;
   }
   store_row_chunk<kFp16>(tile_p, r, c0, pr);
 }
@@ -257,7 +260,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype) {
+cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return cudaErrorNotSupported;
   const cuuint64_t esz = 2;
@@ -265,13 +268,16 @@ cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p
   long long sh_el = t.sh > 0 ? t.sh : (long long)p.tokens * p.head_dim;
   cuuint64_t dims[4] = {(cuuint64_t)p.head_dim, (cuuint64_t)p.tokens, (cuuint64_t)p.heads, (cuuint64_t)p.batch};
   cuuint64_t strides[3] = {(cuuint64_t)t.st * esz, (cuuint64_t)sh_el * esz, (cuuint64_t)sb_el * esz};
-  cuuint32_t box[4] = {64, (cuuint32_t)kBM, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, dtype == SB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                    t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
+
+// The forward for head sizes above 64 works on 256 query rows per CTA (two 128-row tiles sharing the K/V stream).
+int tc_tile(int head_dim, bool backward) { return (!backward && head_dim > 64) ? 256 : kBM; }
 
 bool tc_supported(int dtype, int head_dim, bool backward) {
   (void)backward;
@@ -297,7 +303,7 @@ cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *laun
   *launches += 1;
   const bool f16 = dtype == SB_DTYPE_F16;
   if (p.head_dim <= 64) return f16 ? launch_fwd_t<64, true>(p, dtype, s) : launch_fwd_t<64, false>(p, dtype, s);
-  return f16 ? launch_fwd_t<128, true>(p, dtype, s) : launch_fwd_t<128, false>(p, dtype, s);
+  return launch_tc_fwd256(p, dtype, s);
 }
 
 }  // namespace sb

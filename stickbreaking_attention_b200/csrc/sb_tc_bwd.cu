@@ -22,34 +22,38 @@ namespace sb {
 // factors at a time, which gives the log-space sum through the end of the chunk; (2) last column to first: W is
 // seeded with 2^(r1 + that sum) -- the largest value it takes in the chunk -- and shrinks by (1 - beta) per
 // column, so it only underflows where A rounds to zero anyway; (3) first column to last: the prefix sum of G and
-// dz.  2.3 transcendentals per score (ex2, rcp, lg2 / 4, ex2 / 32).
+// dz.  About 1.5 transcendentals per score (ex2, rcp / 4, lg2 / 4, ex2 / 32).
 // kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
 template <bool kFp16, bool kStoreA, bool kMasked>
 __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], int c0, int r, bool diag,
                                               int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
                                               float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
   float be[32], ri[32];
-  float prod = 1.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const float x = fminf(__uint_as_float(s[i]) * scale2, 30.f);
-    float e = ex2(x);
-    float t1 = 1.f + e;
-    float rinv = rcp(t1);
-    if (kMasked) {
-      const int col = c0 + i;
-      const bool allowed = row_valid && (!diag || (ac ? col <= r : col < r));
-      e = allowed ? e : 0.f;
-      t1 = allowed ? t1 : 1.f;
-      rinv = allowed ? rinv : 1.f;
+  for (int g = 0; g < 8; ++g) {   // four columns share one reciprocal and one logarithm
+    float e[4], t[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      e[i] = ex2(fminf(__uint_as_float(s[4 * g + i]) * scale2, 30.f));
+      t[i] = 1.f + e[i];
+      if (kMasked) {
+        const int col = c0 + 4 * g + i;
+        const bool allowed = row_valid && (!diag || (ac ? col <= r : col < r));
+        e[i] = allowed ? e[i] : 0.f;
+        t[i] = allowed ? t[i] : 1.f;
+      }
     }
-    be[i] = e * rinv;
-    ri[i] = rinv;
-    prod *= t1;
-    if ((i & 3) == 3) {
-      logsum += lg2(prod);
-      prod = 1.f;
-    }
+    const float p01 = t[0] * t[1], p23 = t[2] * t[3];
+    const float prod = p01 * p23;
+    const float rp = rcp(prod);
+    logsum += lg2(prod);
+    const float a = rp * p23, b = rp * p01;
+    ri[4 * g + 0] = a * t[1];
+    ri[4 * g + 1] = a * t[0];
+    ri[4 * g + 2] = b * t[3];
+    ri[4 * g + 3] = b * t[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) be[4 * g + i] = e[i] * ri[4 * g + i];
   }
   float W = ex2(r1 + logsum);
   float pa[32];

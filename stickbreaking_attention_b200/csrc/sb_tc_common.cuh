@@ -63,6 +63,20 @@ __device__ __forceinline__ void store_row_chunk(uint8_t *tile, int r, int c0, co
   }
 }
 
+// Stores 16 consecutive columns (first column c0, a multiple of 16) of row r of such a tile.
+template <bool kFp16>
+__device__ __forceinline__ void store_row_chunk16(uint8_t *tile, int r, int c0, const float (&x)[16]) {
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    uint4 w;
+    w.x = pack2<kFp16>(x[g * 8 + 0], x[g * 8 + 1]);
+    w.y = pack2<kFp16>(x[g * 8 + 2], x[g * 8 + 3]);
+    w.z = pack2<kFp16>(x[g * 8 + 4], x[g * 8 + 5]);
+    w.w = pack2<kFp16>(x[g * 8 + 6], x[g * 8 + 7]);
+    *reinterpret_cast<uint4 *>(tile + sw128_chunk_offset(r, c0 + g * 8)) = w;
+  }
+}
+
 // TMEM accumulator rows (one per thread) -> 16-bit global rows, `mul` applied, columns >= head_dim dropped.
 template <int D, bool kFp16, typename T>
 __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool valid, int head_dim, float mul) {
@@ -88,38 +102,40 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool
   }
 }
 
-// MMA issue helpers (called by one thread).  A K-major [128 x 16*n] operand advances 32 bytes per 16-element
-// K step inside a 64-element block and one box per block; an MN-major one advances 16 rows (2048 bytes).
-template <int KDIM>
+// MMA issue helpers (called by one thread).  The issuing thread is a scalar instruction stream, so descriptors are
+// built once per tile and only their 14-bit start-address field (bytes >> 4) is advanced per instruction:
+// a K-major operand moves 32 bytes per 16-element K step inside a 64-element block and one box per block; an
+// MN-major one moves 16 rows (2048 bytes) per K step.
+__device__ __forceinline__ constexpr uint64_t kstep_kmajor(int k, int box_bytes) {
+  return (uint64_t)(((k >> 2) * box_bytes + (k & 3) * 32) >> 4);
+}
+template <int KDIM, int A_BOX = kBoxBytes, int B_BOX = kBoxBytes>
 __device__ __forceinline__ void mma_kmajor_kmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
                                                   bool accumulate) {
+  const uint64_t a0 = smem_desc_sw128(a_addr, 16, 1024), b0 = smem_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
-  for (int k = 0; k < KDIM / 16; ++k) {
-    const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + off, 16, 1024), smem_desc_sw128(b_addr + off, 16, 1024), idesc,
-               accumulate || k > 0);
-  }
+  for (int k = 0; k < KDIM / 16; ++k)
+    mma_f16_ss(d_tmem, a0 + kstep_kmajor(k, A_BOX), b0 + kstep_kmajor(k, B_BOX), idesc, accumulate || k > 0);
 }
-// A: K-major [128 x 128];  B: rows = K (128), columns = N, MN-major.
+// A: K-major [128 x KDIM];  B: rows = K (KDIM), columns = N in blocks of 64 that are B_BOX bytes apart, MN-major.
+template <int KDIM = kBM, int B_BOX = kBoxBytes>
 __device__ __forceinline__ void mma_kmajor_mnmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
                                                    bool accumulate) {
+  const uint64_t a0 = smem_desc_sw128(a_addr, 16, 1024), b0 = smem_desc_sw128(b_addr, B_BOX, 1024);
 #pragma unroll
-  for (int ks = 0; ks < kBM / 16; ++ks) {
-    const uint32_t aoff = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + aoff, 16, 1024), smem_desc_sw128(b_addr + ks * 2048, kBoxBytes, 1024),
-               idesc, accumulate || ks > 0);
-  }
+  for (int ks = 0; ks < KDIM / 16; ++ks)
+    mma_f16_ss(d_tmem, a0 + kstep_kmajor(ks, kBoxBytes), b0 + (uint64_t)(ks * 128), idesc, accumulate || ks > 0);
 }
 // A and B both stored with rows = K (128): A^T B.
 __device__ __forceinline__ void mma_mnmajor_mnmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
                                                     bool accumulate) {
+  const uint64_t a0 = smem_desc_sw128(a_addr, kBoxBytes, 1024), b0 = smem_desc_sw128(b_addr, kBoxBytes, 1024);
 #pragma unroll
   for (int ks = 0; ks < kBM / 16; ++ks)
-    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + ks * 2048, kBoxBytes, 1024),
-               smem_desc_sw128(b_addr + ks * 2048, kBoxBytes, 1024), idesc, accumulate || ks > 0);
+    mma_f16_ss(d_tmem, a0 + (uint64_t)(ks * 128), b0 + (uint64_t)(ks * 128), idesc, accumulate || ks > 0);
 }
 
 // host: 4-D TMA map (head_dim, tokens, heads, batch), [64 x 128 x 1 x 1] box, 128-byte swizzle, zero fill
-cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype);
+cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows = kBM);
 
 }  // namespace sb

@@ -1,0 +1,295 @@
+// Tensor-core forward kernel for head sizes 72..128: 256 query rows per CTA.
+//
+// Reference counterpart: _forward_one_row, sb_varlen_fwd.py:81-215.  A CTA owns two adjacent 128-row query tiles
+// (a: rows 0..127, b: rows 128..255 of its 256-row block) of one (sequence, head) and streams 64-key K/V
+// sub-tiles from its last needed key back to the sequence start.  Both tiles consume the same K/V stage, so K/V
+// is read once per 256 rows, and the two row-owning warpgroups (warps 0-3: tile a, warps 4-7: tile b) keep two
+// warps resident per scheduler so that one hides the other's dependent-issue and TMEM latency.
+//   warp 8    TMA producer: Q_a, Q_b once, then K/V sub-tiles into a 3-stage ring
+//   warps 9,10 MMA issuers, one per tile: S_x = Q_x K^T (128x64) into a double-buffered TMEM slot, O_x += P_x V
+//   warps 0-7 one thread per query row: p = beta * R with the running product R of (1 - beta) over later keys,
+//             P written as a 16-bit [128 x 64] swizzled tile (double-buffered) for the second MMA
+// TMEM columns: S_a[2] 0..127, S_b[2] 128..255, O_a 256..383, O_b 384..511.  All waits are bounded.
+#include "sb_tc_common.cuh"
+
+namespace sb {
+
+namespace fwd256 {
+constexpr int kThreads = 352;
+constexpr int kBN = 64;                       // keys per sub-tile
+constexpr int kStages = 3;
+constexpr int kQBytes = kBM * 128 * 2;        // one 128-row Q tile (two 128x64 boxes)
+constexpr int kKvBoxBytes = kBN * 64 * 2;     // one 64-row x 64-column box
+constexpr int kKvTileBytes = 2 * kKvBoxBytes; // K or V sub-tile: 64 keys x 128 columns
+constexpr int kStageBytes = 2 * kKvTileBytes; // K and V
+constexpr int kPBytes = kBM * kBN * 2;        // one P buffer: 128 rows x 64 keys
+constexpr int kBarBytes = 512;
+constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
+enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bSEmpty = 11, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 24 };
+// per-warpgroup barrier index: base + wg * 2 + buf
+}  // namespace fwd256
+
+// One row, 32 consecutive key columns of a 64-key sub-tile, last column first (see fwd_row_chunk in sb_tc.cu for
+// the recurrence).  key0: index inside the sequence of the sub-tile's column c0; row: index of this query row.
+template <bool kFp16, bool kMasked>
+__device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0, int key0, int row, int ac,
+                                                 float scale2, float &R, float &logsum, uint8_t *tile_p, int r) {
+  float pr[16];
+#pragma unroll
+  for (int g = 3; g >= 0; --g) {   // four columns at a time, last group first
+    float e[4], t[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      e[i] = ex2(fminf(__uint_as_float(v[4 * g + i]) * scale2, 30.f));
+      t[i] = 1.f + e[i];
+      if (kMasked) {
+        const int key = key0 + 4 * g + i;
+        const bool allowed = ac ? (key <= row) : (key < row);
+        e[i] = allowed ? e[i] : 0.f;
+        t[i] = allowed ? t[i] : 1.f;
+      }
+    }
+    // one reciprocal and one logarithm for the four factors (1 + e): 1/t_i = (1 / t0 t1 t2 t3) * (product of the others)
+    const float p01 = t[0] * t[1], p23 = t[2] * t[3];
+    const float prod = p01 * p23;
+    const float rp = rcp(prod);
+    logsum += lg2(prod);
+    const float a = rp * p23, b = rp * p01;
+    const float ri3 = b * t[2], ri2 = b * t[3], ri1 = a * t[0], ri0 = a * t[1];
+    pr[4 * g + 3] = (e[3] * ri3) * R; R *= ri3;
+    pr[4 * g + 2] = (e[2] * ri2) * R; R *= ri2;
+    pr[4 * g + 1] = (e[1] * ri1) * R; R *= ri1;
+    pr[4 * g + 0] = (e[0] * ri0) * R; R *= ri0;
+  }
+  store_row_chunk16<kFp16>(tile_p, r, c0, pr);
+}
+
+template <bool kFp16>
+__global__ void __launch_bounds__(fwd256::kThreads, 1)
+tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const KParams p) {
+  using namespace fwd256;
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x, true, c)) return;   // c.idx: index of the 256-row block inside the sequence
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  const uint32_t sQ = base;                             // Q_a, Q_b
+  const uint32_t sKV = sQ + 2 * kQBytes;                // stages: K sub-tile then V sub-tile
+  const uint32_t sP = sKV + kStages * kStageBytes;      // P[wg][buf]
+  const uint32_t sBar = sP + 4 * kPBytes;
+  uint8_t *gP = gbase + (sP - base);
+  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
+  volatile int *abort_flag = &ctl->abort;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int tr_cur = 0;   // cursor of this thread's event-log lane (experiments only)
+  const int h = p.head0 + blockIdx.y;
+  const int m = c.idx;
+  const int blk_row0 = m * 256;                          // first row of the block inside the sequence
+  const int n_sub = (c.len + kBN - 1) / kBN;             // 64-key sub-tiles of the sequence
+  const bool b_active = blk_row0 + kBM < c.len;
+  const int s_hi_a = min(4 * m + 1, n_sub - 1);          // last sub-tile tile a needs
+  const int s_hi_b = min(4 * m + 3, n_sub - 1);
+  const int s_top = b_active ? s_hi_b : s_hi_a;
+  const int n_steps = s_top + 1;                         // step t handles sub-tile s_top - t
+  const int t0_a = s_top - s_hi_a;                       // first step in which tile a takes part
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(bQ), 1);
+    const int issuers = b_active ? 2 : 1;   // both MMA issuers release a K/V stage and signal the end
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar(bKvFull + s), 1); mbar_init(bar(bKvEmpty + s), issuers); }
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(bar(bSFull + s), 1);
+      mbar_init(bar(bPFull + s), 4);
+      mbar_init(bar(bPEmpty + s), 1);
+    }
+    mbar_init(bar(bOFull), issuers);
+    ctl->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+      const int qrow = (int)c.tok0 + blk_row0;
+      mbar_arrive_expect_tx(bar(bQ), 2 * kQBytes);
+      for (int t = 0; t < 2; ++t)
+        for (int kb = 0; kb < 2; ++kb)
+          tma_load_4d(sQ + t * kQBytes + kb * kBoxBytes, &tm_q, bar(bQ), kb * 64, qrow + t * kBM, h, (int)c.boff);
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t % kStages;
+        if (t >= kStages && !wait_or_abort(bar(bKvEmpty + st), ((t / kStages) - 1) & 1, abort_flag, p, 310)) break;
+        if (*abort_flag) break;
+        const int krow = (int)c.tok0 + (s_top - t) * kBN;
+        const uint32_t dst = sKV + st * kStageBytes;
+        trace_event(p, 0, tr_cur, 1, t);
+        mbar_arrive_expect_tx(bar(bKvFull + st), kStageBytes);
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(dst + kb * kKvBoxBytes, &tm_k, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
+          tma_load_4d(dst + kKvTileBytes + kb * kKvBoxBytes, &tm_v, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
+        }
+        if (p.dbg == 9) {   // experiment: measure the load latency directly
+          while (!mbar_try_wait(bar(bKvFull + st), (t / kStages) & 1)) {}
+          trace_event(p, 0, tr_cur, 8, t);
+        }
+      }
+    }
+  } else if (warp >= 9) {
+    // ------------------------------------------------ MMA issuers: warp 9 for tile a, warp 10 for tile b
+    const int wg = warp - 9;
+    if (lane == 0 && (wg == 0 || b_active)) {
+      constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);
+      constexpr uint32_t idesc_pv = idesc_f16(kBM, D, kFp16, false, true);
+      const int t0 = wg == 0 ? t0_a : 0;
+      const int my_steps = n_steps - t0;
+      const uint32_t qaddr = sQ + wg * kQBytes;
+      // tile a does not read the first t0_a stages: release them on its behalf
+      for (int t = 0; t < t0; ++t) mbar_arrive(bar(bKvEmpty + t % kStages));
+      bool ok = wait_or_abort(bar(bQ), 0, abort_flag, p, 320);
+      // Iteration u issues S(u) and then P V of step u-1, so that the next scores are being computed while the
+      // rows of the current step are processed.  S(u) reuses the TMEM slot of step u-2, whose rows were finished
+      // before p_full(u-2) was signalled, and that was waited for in iteration u-1.
+      for (int u = 0; ok && u <= my_steps; ++u) {
+        if (u < my_steps) {
+          const int t = t0 + u, st = t % kStages;
+          ok = wait_or_abort(bar(bKvFull + st), (t / kStages) & 1, abort_flag, p, 321);
+          if (!ok) break;
+          trace_event(p, 1 + 3 * wg, tr_cur, 2 + 16 * wg, t);
+          tc_fence_after();
+          mma_kmajor_kmajor<D, kBoxBytes, kKvBoxBytes>(tmem + wg * 128 + (u & 1) * 64, qaddr, sKV + st * kStageBytes, idesc_s,
+                                                       false);
+          mma_commit(bar(bSFull + wg * 2 + (u & 1)));
+          trace_event(p, 1 + 3 * wg, tr_cur, 3 + 16 * wg, t);
+        }
+        if (u >= 1) {
+          const int up = u - 1, t = t0 + up, st = t % kStages;
+          ok = wait_or_abort(bar(bPFull + wg * 2 + (up & 1)), (up >> 1) & 1, abort_flag, p, 323);
+          if (!ok) break;
+          trace_event(p, 1 + 3 * wg, tr_cur, 6 + 16 * wg, t);
+          tc_fence_after();
+          // 16 keys per MMA; V: 64 rows x (2 x 64) columns, MN-major
+          mma_kmajor_mnmajor<kBN, kKvBoxBytes>(tmem + 256 + wg * 128, sP + (wg * 2 + (up & 1)) * kPBytes,
+                                               sKV + st * kStageBytes + kKvTileBytes, idesc_pv, up > 0);
+          mma_commit(bar(bPEmpty + wg * 2 + (up & 1)));
+          mma_commit(bar(bKvEmpty + st));
+          trace_event(p, 1 + 3 * wg, tr_cur, 7 + 16 * wg, t);
+        }
+      }
+      if (ok) mma_commit(bar(bOFull));
+    }
+  } else {
+    // ------------------------------------------------ one thread per query row, one warpgroup per 128-row tile
+    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
+    const int wg = warp >> 2;
+    const int r = threadIdx.x & 127;                 // row inside the tile == TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const float scale2 = p.scale * kLog2e;
+    const int ac = p.attend_current;
+    const int row = blk_row0 + wg * kBM + r;         // row index inside the sequence
+    const int t0 = wg == 0 ? t0_a : 0;
+    const int my_steps = (wg == 1 && !b_active) ? 0 : n_steps - t0;
+    const int s_diag0 = 4 * m + 2 * wg;              // first sub-tile that reaches this tile's diagonal band
+    double run = 0.0;
+    bool ok = true;
+    for (int u = 0; u < my_steps && ok; ++u) {
+      const int s = s_top - (t0 + u);
+      const int buf = u & 1;
+      ok = wait_or_abort(bar(bSFull + wg * 2 + buf), (u >> 1) & 1, abort_flag, p, 330);
+      if (ok && u >= 2) ok = wait_or_abort(bar(bPEmpty + wg * 2 + buf), ((u >> 1) - 1) & 1, abort_flag, p, 331);
+      if (!ok) break;
+      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 4 + 16 * wg, t0 + u);
+      tc_fence_after();
+      const uint32_t ts = tmem + wg * 128 + buf * 64 + lane_off;
+      uint8_t *tile_p = gP + (wg * 2 + buf) * kPBytes;
+      if (p.dbg == 5) {   // experiment: no row work at all, only the barrier protocol
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(bPFull + wg * 2 + buf));
+        continue;
+      }
+      float R = ex2(-(float)run);
+      float logsum = 0.f;
+      // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
+      if (s >= s_diag0) {
+#pragma unroll 1
+        for (int ch = 3; ch >= 0; --ch) {
+          uint32_t v[16];
+          tmem_ld16(ts + ch * 16, v);
+          tmem_wait_ld_regs(v);
+          fwd256_row_chunk<kFp16, true>(v, ch * 16, s * kBN + ch * 16, row, ac, scale2, R, logsum, tile_p, r);
+        }
+      } else {
+        uint32_t va[16], vb[16];
+        tmem_ld16(ts + 48, va);
+#pragma unroll 1
+        for (int pair = 1; pair >= 0; --pair) {
+          tmem_wait_ld_regs(va);
+          tmem_ld16(ts + pair * 32, vb);
+          fwd256_row_chunk<kFp16, false>(va, pair * 32 + 16, 0, 0, ac, scale2, R, logsum, tile_p, r);
+          tmem_wait_ld_regs(vb);
+          if (pair == 1) tmem_ld16(ts + 16, va);
+          fwd256_row_chunk<kFp16, false>(vb, pair * 32, 0, 0, ac, scale2, R, logsum, tile_p, r);
+        }
+      }
+      run += (double)logsum;
+      tc_fence_before();          // this step's TMEM reads are done before the slot is handed back
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bPFull + wg * 2 + buf));
+      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 5 + 16 * wg, t0 + u);
+    }
+    // ---- epilogue: O (TMEM) -> global, rem, log_rem
+    if (ok && my_steps > 0) ok = wait_or_abort(bar(bOFull), 0, abort_flag, p, 332);
+    if (ok && my_steps > 0) {
+      tc_fence_after();
+      const bool valid = row < c.len;
+      T *orow = reinterpret_cast<T *>(p.o.ptr) + c.boff * p.o.sb + (long long)h * p.o.sh + (c.tok0 + row) * p.o.st;
+      store_acc_rows<D, kFp16, T>(tmem + 256 + wg * 128 + lane_off, orow, valid, p.head_dim, 1.f);
+      if (valid) {
+        const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + row;
+        reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(ex2(-(float)run));
+        p.log_rem[idx] = -run;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+}
+
+cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s) {
+  CUtensorMap mq, mk, mv;
+  cudaError_t e;
+  if ((e = make_tile_map(&mq, p.q, p, dtype, kBM)) != cudaSuccess) return e;
+  if ((e = make_tile_map(&mk, p.k, p, dtype, fwd256::kBN)) != cudaSuccess) return e;
+  if ((e = make_tile_map(&mv, p.v, p, dtype, fwd256::kBN)) != cudaSuccess) return e;
+  dim3 grid(p.tiles_cap, p.head_cnt);
+  if (dtype == SB_DTYPE_F16) {
+    auto kernel = tc_fwd256_kernel<true>;
+    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
+    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, p);
+  } else {
+    auto kernel = tc_fwd256_kernel<false>;
+    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
+    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace sb
