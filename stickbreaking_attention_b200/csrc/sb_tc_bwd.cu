@@ -14,23 +14,24 @@
 
 namespace sb {
 
-// One row, 32 consecutive key columns starting at c0.  s: raw q.k accumulators, dp: <dO_i, v_j>.
+// One row, 16 consecutive key columns starting at c0.  s: raw q.k accumulators, dp: <dO_i, v_j>.
 //   x = z log2(e), clamped at 30;  e = 2^x;  1 - beta = 1 / (1 + e);  beta = e / (1 + e)
 //   A_j = beta_j * W_j,  W_j = product of (1 - beta) over the allowed keys after j up to the diagonal
 //   G = A (dP - dR);  C = gpre + inclusive prefix of G;  dz = G - beta C
-// Three sweeps over the 32 columns, all in registers: (1) e and 1/(1+e), and log2 of the product of (1 + e) four
-// factors at a time, which gives the log-space sum through the end of the chunk; (2) last column to first: W is
-// seeded with 2^(r1 + that sum) -- the largest value it takes in the chunk -- and shrinks by (1 - beta) per
-// column, so it only underflows where A rounds to zero anyway; (3) first column to last: the prefix sum of G and
-// dz.  About 1.5 transcendentals per score (ex2, rcp / 4, lg2 / 4, ex2 / 32).
+// Three sweeps over the 16 columns, all in registers: (1) e and 1/(1+e) -- four columns share one reciprocal and
+// one logarithm of the product of their (1 + e), which gives the log-space sum through the end of the chunk;
+// (2) last column to first: W is seeded with 2^(r1 + that sum) -- the largest value it takes in the chunk -- and
+// shrinks by (1 - beta) per column, so it only underflows where A rounds to zero anyway; (3) first column to last:
+// the prefix sum of G and dz.  About 1.6 transcendentals per score (ex2, rcp / 4, lg2 / 4, ex2 / 16).
 // kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
+// The chunk is kept to 16 columns so that the unrolled code of all variants stays inside the instruction cache.
 template <bool kFp16, bool kStoreA, bool kMasked>
-__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], int c0, int r, bool diag,
+__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uint32_t (&dp)[16], int c0, int r, bool diag,
                                               int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
                                               float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
-  float be[32], ri[32];
+  float be[16], ri[16];
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {   // four columns share one reciprocal and one logarithm
+  for (int g = 0; g < 4; ++g) {
     float e[4], t[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -56,15 +57,15 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[32], const uin
     for (int i = 0; i < 4; ++i) be[4 * g + i] = e[i] * ri[4 * g + i];
   }
   float W = ex2(r1 + logsum);
-  float pa[32];
+  float pa[16];
 #pragma unroll
-  for (int i = 31; i >= 0; --i) {
+  for (int i = 15; i >= 0; --i) {
     pa[i] = be[i] * W;
     W *= ri[i];
   }
-  float pz[32];
+  float pz[16];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
+  for (int i = 0; i < 16; ++i) {
     float g = pa[i] * (__uint_as_float(dp[i]) - dr);
     if (kMasked) {   // rows past the sequence end carry arbitrary values: select, do not rely on 0 * x
       const int col = c0 + i;
@@ -76,36 +77,36 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[32], const uin
     pz[i] = fmaf(-be[i], gpre + gs, g);
     if (kMasked) pz[i] = row_valid ? pz[i] : 0.f;
   }
-  if constexpr (kStoreA) store_row_chunk<kFp16>(tile_a, r, c0, pa);
-  store_row_chunk<kFp16>(tile_z, r, c0, pz);
+  if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
+  store_row_chunk16<kFp16>(tile_z, r, c0, pz);
 }
 
 // One row of a 128-key tile.  `empty_bar` is signalled (one arrival per warp) as soon as the last columns of S and
-// dP are in registers.  The plain version reads TMEM one 32-column load ahead of the arithmetic.
+// dP are in registers.  The plain version reads TMEM one 16-column load ahead of the arithmetic.
 template <bool kFp16, bool kStoreA>
 __device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r, float scale2,
                                              float r1, float gpre, float dr, float &gs, float &logsum, uint8_t *tile_a,
                                              uint8_t *tile_z) {
-  uint32_t s0[32], d0[32], s1[32], d1[32];
-  tmem_ld32(ts, s0);
-  tmem_ld32(tp, d0);
+  uint32_t s0[16], d0[16], s1[16], d1[16];
+  tmem_ld16(ts, s0);
+  tmem_ld16(tp, d0);
 #pragma unroll 1
-  for (int pair = 0; pair < 2; ++pair) {
-    const int c0 = pair * 64;
+  for (int pair = 0; pair < 4; ++pair) {
+    const int c0 = pair * 32;
     tmem_wait_ld_regs(s0, d0);
-    tmem_ld32(ts + c0 + 32, s1);
-    tmem_ld32(tp + c0 + 32, d1);
+    tmem_ld16(ts + c0 + 16, s1);
+    tmem_ld16(tp + c0 + 16, d1);
     bwd_row_chunk<kFp16, kStoreA, false>(s0, d0, c0, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
     tmem_wait_ld_regs(s1, d1);
-    if (pair == 0) {
-      tmem_ld32(ts + 64, s0);
-      tmem_ld32(tp + 64, d0);
+    if (pair < 3) {
+      tmem_ld16(ts + c0 + 32, s0);
+      tmem_ld16(tp + c0 + 32, d0);
     } else {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar);
     }
-    bwd_row_chunk<kFp16, kStoreA, false>(s1, d1, c0 + 32, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    bwd_row_chunk<kFp16, kStoreA, false>(s1, d1, c0 + 16, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
   }
 }
 
@@ -114,17 +115,17 @@ __device__ __forceinline__ void bwd_row_pass_masked(uint32_t ts, uint32_t tp, ui
                                                     bool diag, int ac, bool row_valid, float scale2, float r1, float gpre,
                                                     float dr, float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
 #pragma unroll 1
-  for (int ch = 0; ch < 4; ++ch) {
-    uint32_t s0[32], d0[32];
-    tmem_ld32(ts + ch * 32, s0);
-    tmem_ld32(tp + ch * 32, d0);
+  for (int ch = 0; ch < 8; ++ch) {
+    uint32_t s0[16], d0[16];
+    tmem_ld16(ts + ch * 16, s0);
+    tmem_ld16(tp + ch * 16, d0);
     tmem_wait_ld_regs(s0, d0);
-    if (ch == 3) {
+    if (ch == 7) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar);
     }
-    bwd_row_chunk<kFp16, kStoreA, true>(s0, d0, ch * 32, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    bwd_row_chunk<kFp16, kStoreA, true>(s0, d0, ch * 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
   }
 }
 
