@@ -23,7 +23,7 @@ static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; 
 
 // Workspace layout, a pure function of the shapes:
 //   [hdr 256 B][tile_prefix int32 x (num_seq+1)][pair_prefix int64 x (num_seq+1)]
-//   backward only: [R1 fp32 x chunk_heads x pairs_cap x tile][S2 same]
+//   backward only: [R1 fp32 x chunk_heads x pairs_cap x halves x tile][S2 same]
 struct Plan {
   int path;
   int tile;
@@ -32,6 +32,7 @@ struct Plan {
   int max_seqlen;
   long long pairs_cap;
   size_t off_tile_prefix, off_pair_prefix, off_bnd;
+  int bnd_halves;             // boundary records per (query tile, key tile) pair
   size_t bnd_bytes_per_head;  // one of the two arrays
   int chunk_heads;
   size_t total_fwd, total_bwd;
@@ -92,7 +93,9 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   pl.off_tile_prefix = 256;
   pl.off_pair_prefix = align_up(pl.off_tile_prefix + sizeof(int) * (size_t)(p->num_seq + 1), 256);
   pl.off_bnd = align_up(pl.off_pair_prefix + sizeof(long long) * (size_t)(p->num_seq + 1), 256);
-  pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * sizeof(float), 256);
+  // the tensor-core path records the carried values twice per 128-key tile (at keys 0 and 64)
+  pl.bnd_halves = tc ? 2 : 1;
+  pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * pl.bnd_halves * sizeof(float), 256);
   size_t chunk = pl.bnd_bytes_per_head ? kBoundaryBudget / (2 * pl.bnd_bytes_per_head) : (size_t)p->heads;
   if (chunk < 1) chunk = 1;
   if (chunk > (size_t)p->heads) chunk = p->heads;
@@ -169,7 +172,7 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   k.pair_prefix = reinterpret_cast<long long *>(ws + pl.off_pair_prefix);
   k.bnd_r1 = reinterpret_cast<float *>(ws + pl.off_bnd);
   k.bnd_s2 = reinterpret_cast<float *>(ws + pl.off_bnd + pl.bnd_bytes_per_head * pl.chunk_heads);
-  k.pairs_cap = (long long)(pl.bnd_bytes_per_head / ((size_t)pl.tile * sizeof(float)));
+  k.pairs_cap = (long long)(pl.bnd_bytes_per_head / ((size_t)pl.tile * pl.bnd_halves * sizeof(float)));
   k.status = p->status;
   return SB_OK;
 }

@@ -44,8 +44,7 @@ __device__ __forceinline__ void fwd_row_chunk(const uint32_t (&v)[32], int c0, i
       e[i] = ex2(fminf(__uint_as_float(v[4 * g + i]) * scale2, 30.f));
       t[i] = 1.f + e[i];
       if (kDiag) {
-        const int col = c0 + 4 * g + i;
-        const bool allowed = ac ? (col <= r) : (col < r);
+        const bool allowed = c0 + 4 * g + i < r + ac;
         e[i] = allowed ? e[i] : 0.f;
         t[i] = allowed ? t[i] : 1.f;
       }

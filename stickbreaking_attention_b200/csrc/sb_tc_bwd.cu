@@ -26,9 +26,11 @@ namespace sb {
 // kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
 // The chunk is kept to 16 columns so that the unrolled code of all variants stays inside the instruction cache.
 template <bool kFp16, bool kStoreA, bool kMasked>
-__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uint32_t (&dp)[16], int c0, int r, bool diag,
+__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uint32_t (&dp)[16], int c0, int mc0, int r, bool diag,
                                               int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
                                               float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+  // columns (tile-local key indices) below `limit` are allowed: one compare per column, no branches
+  const int limit = !row_valid ? -1 : (diag ? r + ac : 0x7fffffff);
   float be[16], ri[16];
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
@@ -38,8 +40,7 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
       e[i] = ex2(fminf(__uint_as_float(s[4 * g + i]) * scale2, 30.f));
       t[i] = 1.f + e[i];
       if (kMasked) {
-        const int col = c0 + 4 * g + i;
-        const bool allowed = row_valid && (!diag || (ac ? col <= r : col < r));
+        const bool allowed = mc0 + 4 * g + i < limit;   // mc0: key index inside the 128-key tile (c0 addresses the output)
         e[i] = allowed ? e[i] : 0.f;
         t[i] = allowed ? t[i] : 1.f;
       }
@@ -68,8 +69,7 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
   for (int i = 0; i < 16; ++i) {
     float g = pa[i] * (__uint_as_float(dp[i]) - dr);
     if (kMasked) {   // rows past the sequence end carry arbitrary values: select, do not rely on 0 * x
-      const int col = c0 + i;
-      const bool allowed = row_valid && (!diag || (ac ? col <= r : col < r));
+      const bool allowed = mc0 + i < limit;
       g = allowed ? g : 0.f;
       pa[i] = allowed ? pa[i] : 0.f;
     }
@@ -86,7 +86,7 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
 template <bool kFp16, bool kStoreA>
 __device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r, float scale2,
                                              float r1, float gpre, float dr, float &gs, float &logsum, uint8_t *tile_a,
-                                             uint8_t *tile_z) {
+                                             uint8_t *tile_z, float *mid_r1, float *mid_s2) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
   tmem_ld16(ts, s0);
   tmem_ld16(tp, d0);
@@ -96,7 +96,7 @@ __device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t 
     tmem_wait_ld_regs(s0, d0);
     tmem_ld16(ts + c0 + 16, s1);
     tmem_ld16(tp + c0 + 16, d1);
-    bwd_row_chunk<kFp16, kStoreA, false>(s0, d0, c0, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    bwd_row_chunk<kFp16, kStoreA, false>(s0, d0, c0, c0, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
     tmem_wait_ld_regs(s1, d1);
     if (pair < 3) {
       tmem_ld16(ts + c0 + 32, s0);
@@ -106,14 +106,19 @@ __device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t 
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar);
     }
-    bwd_row_chunk<kFp16, kStoreA, false>(s1, d1, c0 + 16, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    bwd_row_chunk<kFp16, kStoreA, false>(s1, d1, c0 + 16, c0 + 16, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    if (pair == 1 && mid_r1 != nullptr) {   // the carried values at key 64 of the tile
+      *mid_r1 = r1 + logsum;
+      *mid_s2 = gpre + gs;
+    }
   }
 }
 
 template <bool kFp16, bool kStoreA>
 __device__ __forceinline__ void bwd_row_pass_masked(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r,
                                                     bool diag, int ac, bool row_valid, float scale2, float r1, float gpre,
-                                                    float dr, float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+                                                    float dr, float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z,
+                                                    float *mid_r1, float *mid_s2) {
 #pragma unroll 1
   for (int ch = 0; ch < 8; ++ch) {
     uint32_t s0[16], d0[16];
@@ -125,7 +130,11 @@ __device__ __forceinline__ void bwd_row_pass_masked(uint32_t ts, uint32_t tp, ui
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar);
     }
-    bwd_row_chunk<kFp16, kStoreA, true>(s0, d0, ch * 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    bwd_row_chunk<kFp16, kStoreA, true>(s0, d0, ch * 16, ch * 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    if (ch == 3 && mid_r1 != nullptr) {
+      *mid_r1 = r1 + logsum;
+      *mid_s2 = gpre + gs;
+    }
   }
 }
 
@@ -256,7 +265,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     double r1 = valid ? p.log_rem[idx] : 0.0;   // sum of log2(1-beta) over the keys from the current tile on
     const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]) : 0.f;
     float gpre = 0.f;
-    const long long slot0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * kBM + r;
+    // boundary records: [pair][half: keys 0.. / keys 64..][row]
+    const long long slot0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (2 * kBM) + r;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       ok = wait_or_abort(bar(qSpFull), j & 1, abort_flag, p, 130);
@@ -264,15 +274,17 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const float r1f = (float)r1;
-      p.bnd_r1[slot0 + (long long)j * kBM] = r1f;
-      p.bnd_s2[slot0 + (long long)j * kBM] = gpre;
+      float *rec_r1 = p.bnd_r1 + slot0 + (long long)j * (2 * kBM);
+      float *rec_s2 = p.bnd_s2 + slot0 + (long long)j * (2 * kBM);
+      rec_r1[0] = r1f;
+      rec_s2[0] = gpre;
       float gs = 0.f, logsum = 0.f;
       if (j == I)
         bwd_row_pass_masked<kFp16, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, true, p.attend_current, true,
-                                          scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ);
+                                          scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
       else
         bwd_row_pass<kFp16, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, scale2, r1f, gpre, dr, gs, logsum,
-                                   nullptr, gZ);
+                                   nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
       r1 += (double)logsum;
       gpre += gs;
       fence_proxy_async_smem();
@@ -428,7 +440,7 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int I = J + i;
       const int gi = I * kBM + r;
       const bool valid = gi < c.len;
-      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * kBM + r;
+      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * (2 * kBM) + r;
       const float r1f = p.bnd_r1[slot];
       const float gpre = p.bnd_s2[slot];
       const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(
@@ -439,12 +451,12 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after();
       float gs = 0.f, logsum = 0.f;
       const bool diag = (i == 0);
-      if (diag || I == c.n_tiles - 1)
+      if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0))
         bwd_row_pass_masked<kFp16, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, diag, p.attend_current, valid,
-                                         scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+                                         scale2, r1f, gpre, dr, gs, logsum, gA, gZ, nullptr, nullptr);
       else
         bwd_row_pass<kFp16, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, scale2, r1f, gpre, dr, gs, logsum,
-                                  gA, gZ);
+                                  gA, gZ, nullptr, nullptr);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(vAzFull));
@@ -466,6 +478,238 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp == 5) tmem_dealloc(tmem, kTmemCols);
 }
 
+// =======================================================================================================
+// dkv kernel for head sizes 72..128: one CTA per 64-key strip
+// =======================================================================================================
+// The strip's K and V stay in shared memory; the query tiles from the strip's own tile to the end of the sequence
+// stream through two Q/dO stages.  Two row-owning warpgroups take the query tiles in turn (tile i goes to warpgroup
+// i & 1, which also owns stage i & 1, its own S/dP slots in TMEM, its own A/dz tiles and its own MMA issuer), so two
+// warps are resident per scheduler and one tile's MMAs overlap the other tile's row pass.  Per tile:
+//   S = Q K^T, dP = dO V^T (128 x 64);  row pass restarted from the R1/S2 record of this strip;  then, transposed so
+//   that the MMA's M is the head dimension,  dK^T += Q^T dz  and  dV^T += dO^T A  (128 x 64, one pair per warpgroup).
+// TMEM columns: S_a 0, dP_a 64, S_b 128, dP_b 192, dK^T_a 256, dV^T_a 320, dK^T_b 384, dV^T_b 448.
+namespace dkv2 {
+constexpr int kThreads = 352;            // warps 0-7 rows, warp 8 TMA, warps 9-10 MMA issuers
+constexpr int kBN = 64;
+constexpr int kTileBytes = kBM * 128 * 2;      // Q or dO tile, 128 rows
+constexpr int kStripBytes = kBN * 128 * 2;     // K or V strip, 64 rows: two 64x64 boxes
+constexpr int kStripBox = kBN * 64 * 2;
+constexpr int kAzBytes = kBM * kBN * 2;        // A or dz tile, 128 rows x 64 keys
+constexpr int kSmem = 1024 + 2 * kStripBytes + 4 * kTileBytes + 4 * kAzBytes + 512;
+enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 9, bOutFull = 11, bNum = 12 };
+}  // namespace dkv2
+
+template <bool kFp16>
+__global__ void __launch_bounds__(dkv2::kThreads, 1)
+tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
+  using namespace dkv2;
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x >> 1, false, c)) return;
+  const int half = blockIdx.x & 1;
+  const int J = c.idx;                         // 128-key tile of the strip
+  const int key0 = J * kBM + half * kBN;       // first key of the strip inside the sequence
+  if (key0 >= c.len) return;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  const uint32_t sK = base;
+  const uint32_t sV = sK + kStripBytes;
+  const uint32_t sQ = sV + kStripBytes;              // stage w: Q at sQ + w * 2 * kTileBytes, dO right behind it
+  const uint32_t sAZ = sQ + 4 * kTileBytes;          // warpgroup w: A at sAZ + w * 2 * kAzBytes, dz right behind it
+  const uint32_t sBar = sAZ + 4 * kAzBytes;
+  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
+  volatile int *abort_flag = &ctl->abort;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int tr_cur = 0;   // cursor of this thread's event-log lane (experiments only)
+  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int cnt = c.n_tiles - J;               // query tiles J .. n_tiles-1
+  const int issuers = cnt >= 2 ? 2 : 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(bKV), 1);
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(bar(bQgFull + w), 1);
+      mbar_init(bar(bQgEmpty + w), 1);
+      mbar_init(bar(bSpFull + w), 1);
+      mbar_init(bar(bAzFull + w), 4);
+      mbar_init(bar(bAzEmpty + w), 1);
+    }
+    mbar_init(bar(bOutFull), issuers);
+    ctl->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
+      const int krow = (int)c.tok0 + key0;
+      mbar_arrive_expect_tx(bar(bKV), 2 * kStripBytes);
+      for (int kb = 0; kb < 2; ++kb) {
+        tma_load_4d(sK + kb * kStripBox, &tm_k, bar(bKV), kb * 64, krow, h, (int)c.boff);
+        tma_load_4d(sV + kb * kStripBox, &tm_v, bar(bKV), kb * 64, krow, h, (int)c.boff);
+      }
+      for (int i = 0; i < cnt; ++i) {
+        const int w = i & 1, u = i >> 1;
+        if (u >= 1 && !wait_or_abort(bar(bQgEmpty + w), (u - 1) & 1, abort_flag, p, 410)) break;
+        if (*abort_flag) break;
+        const int qrow = (int)c.tok0 + (J + i) * kBM;
+        const uint32_t dst = sQ + w * 2 * kTileBytes;
+        trace_event(p, 0, tr_cur, 1, i);
+        mbar_arrive_expect_tx(bar(bQgFull + w), 2 * kTileBytes);
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(dst + kb * kBoxBytes, &tm_q, bar(bQgFull + w), kb * 64, qrow, h, (int)c.boff);
+          tma_load_4d(dst + kTileBytes + kb * kBoxBytes, &tm_g, bar(bQgFull + w), kb * 64, qrow, h, (int)c.boff);
+        }
+      }
+    }
+  } else if (warp >= 9) {
+    // ------------------------------------------------ MMA issuers, one per warpgroup
+    const int w = warp - 9;
+    if (lane == 0 && w < issuers) {
+      constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);   // [128 q x 64 keys], both K-major
+      constexpr uint32_t idesc_t = idesc_f16(kBM, kBN, kFp16, true, true);     // [128 d x 64 keys], both MN-major
+      const uint32_t qaddr = sQ + w * 2 * kTileBytes, gaddr = qaddr + kTileBytes;
+      const uint32_t aaddr = sAZ + w * 2 * kAzBytes, zaddr = aaddr + kAzBytes;
+      const uint32_t tS = tmem + w * 128, tP = tS + 64, tDK = tmem + 256 + w * 128, tDV = tDK + 64;
+      const int my_cnt = (cnt - w + 1) >> 1;        // tiles w, w+2, ...
+      bool ok = wait_or_abort(bar(bKV), 0, abort_flag, p, 420);
+      for (int u = 0; ok && u < my_cnt; ++u) {
+        ok = wait_or_abort(bar(bQgFull + w), u & 1, abort_flag, p, 421);
+        if (!ok) break;
+        trace_event(p, 1 + 3 * w, tr_cur, 2 + 16 * w, 2 * u + w);
+        tc_fence_after();
+        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tS, qaddr, sK, idesc_s, false);   // S = Q K^T
+        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tP, gaddr, sV, idesc_s, false);   // dP = dO V^T
+        mma_commit(bar(bSpFull + w));
+        trace_event(p, 1 + 3 * w, tr_cur, 3 + 16 * w, 2 * u + w);
+        ok = wait_or_abort(bar(bAzFull + w), u & 1, abort_flag, p, 422);
+        if (!ok) break;
+        trace_event(p, 1 + 3 * w, tr_cur, 6 + 16 * w, 2 * u + w);
+        tc_fence_after();
+        {   // dK^T += Q^T dz,  dV^T += dO^T A: A operand rows = K (queries), M = d in two 64-blocks; B rows = K, N = 64 keys
+          const uint64_t q0 = smem_desc_sw128(qaddr, kBoxBytes, 1024), g0 = smem_desc_sw128(gaddr, kBoxBytes, 1024);
+          const uint64_t z0 = smem_desc_sw128(zaddr, 16, 1024), a0 = smem_desc_sw128(aaddr, 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < kBM / 16; ++ks) mma_f16_ss(tDK, q0 + (uint64_t)(ks * 128), z0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < kBM / 16; ++ks) mma_f16_ss(tDV, g0 + (uint64_t)(ks * 128), a0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
+        }
+        mma_commit(bar(bQgEmpty + w));
+        mma_commit(bar(bAzEmpty + w));
+        trace_event(p, 1 + 3 * w, tr_cur, 7 + 16 * w, 2 * u + w);
+      }
+      if (ok) mma_commit(bar(bOutFull));
+    }
+  } else {
+    // ------------------------------------------------ rows: warpgroup w takes query tiles w, w+2, ...
+    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
+    const int w = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const float scale2 = p.scale * kLog2e;
+    uint8_t *gA = gbase + (sAZ - base) + w * 2 * kAzBytes;
+    uint8_t *gZ = gA + kAzBytes;
+    const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
+    bool ok = true;
+    for (int i = w, u = 0; i < cnt && ok; i += 2, ++u) {
+      const int I = J + i;
+      const int gi = I * kBM + r;
+      const bool valid = gi < c.len;
+      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 2 + half) * kBM + r;
+      const float r1f = p.bnd_r1[slot];
+      const float gpre = p.bnd_s2[slot];
+      const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(
+                                   p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
+      ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 430);
+      if (ok && u >= 1) ok = wait_or_abort(bar(bAzEmpty + w), (u - 1) & 1, abort_flag, p, 431);
+      if (!ok) break;
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, i);
+      tc_fence_after();
+      float gs = 0.f, logsum = 0.f;
+      const bool diag = (i == 0);
+      if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0)) {
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t s0[16], d0[16];
+          tmem_ld16(tS + ch * 16, s0);
+          tmem_ld16(tP + ch * 16, d0);
+          tmem_wait_ld_regs(s0, d0);
+          bwd_row_chunk<kFp16, true, true>(s0, d0, ch * 16, half * kBN + ch * 16, r, diag, p.attend_current, valid, scale2,
+                                           r1f, gpre, dr, gs, logsum, gA, gZ);
+        }
+      } else {
+        uint32_t s0[16], d0[16], s1[16], d1[16];
+        tmem_ld16(tS, s0);
+        tmem_ld16(tP, d0);
+#pragma unroll 1
+        for (int pair = 0; pair < 2; ++pair) {
+          const int c0 = pair * 32;
+          tmem_wait_ld_regs(s0, d0);
+          tmem_ld16(tS + c0 + 16, s1);
+          tmem_ld16(tP + c0 + 16, d1);
+          bwd_row_chunk<kFp16, true, false>(s0, d0, c0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+          tmem_wait_ld_regs(s1, d1);
+          if (pair == 0) {
+            tmem_ld16(tS + 32, s0);
+            tmem_ld16(tP + 32, d0);
+          }
+          bwd_row_chunk<kFp16, true, false>(s1, d1, c0 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+        }
+      }
+      tc_fence_before();          // this tile's TMEM reads are done before the slots are handed back
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bAzFull + w));
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, i);
+    }
+    // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys
+    if (ok) ok = wait_or_abort(bar(bOutFull), 0, abort_flag, p, 432);
+    if (ok) {
+      tc_fence_after();
+      const TensorRef &out = w == 0 ? p.dk : p.dv;
+      const float mul = w == 0 ? p.scale : 1.f;
+      T *obase = reinterpret_cast<T *>(out.ptr) + c.boff * out.sb + (long long)h * out.sh + (c.tok0 + key0) * out.st + r;
+      const uint32_t t_a = tmem + 256 + w * 64 + lane_off;          // dK^T_a or dV^T_a
+      const uint32_t t_b = t_a + 128;                               // the other warpgroup's partial sums
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t va[16], vb[16];
+        tmem_ld16(t_a + ch * 16, va);
+        if (issuers == 2) tmem_ld16(t_b + ch * 16, vb);
+        tmem_wait_ld();
+        if (r < p.head_dim) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const int key = key0 + ch * 16 + k;
+            float x = __uint_as_float(va[k]);
+            if (issuers == 2) x += __uint_as_float(vb[k]);
+            if (key < c.len) obase[(long long)(ch * 16 + k) * out.st] = from_f32<T>(x * mul);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+}
+
 // -------------------------------------------------------------------------------------------------------
 template <int D, bool kFp16>
 static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
@@ -483,7 +727,17 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     kernel<<<grid, kTcThreads, DqCfg<D>::kSmem, s>>>(mq, mk, mv, mg, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
-  if (!p.skip_dkv) {
+  if (!p.skip_dkv && D == 128) {
+    CUtensorMap mk64, mv64;
+    if ((e = make_tile_map(&mk64, p.k, p, dtype, dkv2::kBN)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mv64, p.v, p, dtype, dkv2::kBN)) != cudaSuccess) return e;
+    auto kernel = tc_bwd_dkv2_kernel<kFp16>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv2::kSmem);
+    if (e != cudaSuccess) return e;
+    dim3 grid2(2 * p.tiles_cap, p.head_cnt);
+    kernel<<<grid2, dkv2::kThreads, dkv2::kSmem, s>>>(mq, mk64, mv64, mg, p);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  } else if (!p.skip_dkv) {
     auto kernel = tc_bwd_dkv_kernel<D, kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::kSmem);
     if (e != cudaSuccess) return e;

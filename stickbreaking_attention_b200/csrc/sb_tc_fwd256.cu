@@ -43,8 +43,7 @@ __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0
       e[i] = ex2(fminf(__uint_as_float(v[4 * g + i]) * scale2, 30.f));
       t[i] = 1.f + e[i];
       if (kMasked) {
-        const int key = key0 + 4 * g + i;
-        const bool allowed = ac ? (key <= row) : (key < row);
+        const bool allowed = key0 + 4 * g + i < row + ac;
         e[i] = allowed ? e[i] : 0.f;
         t[i] = allowed ? t[i] : 1.f;
       }
