@@ -82,11 +82,13 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
 }
 
 // One row of a 128-key tile.  `empty_bar` is signalled (one arrival per warp) as soon as the last columns of S and
-// dP are in registers.  The plain version reads TMEM one 16-column load ahead of the arithmetic.
-template <bool kFp16, bool kStoreA>
-__device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r, float scale2,
-                                             float r1, float gpre, float dr, float &gs, float &logsum, uint8_t *tile_a,
-                                             uint8_t *tile_z, float *mid_r1, float *mid_s2) {
+// dP are in registers.  TMEM is read one 16-column load ahead of the arithmetic.  mid_r1 / mid_s2 (optional)
+// receive the carried values at key 64 of the tile.
+template <bool kFp16, bool kStoreA, bool kMasked>
+__device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r, bool diag,
+                                             int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
+                                             float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z, float *mid_r1,
+                                             float *mid_s2) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
   tmem_ld16(ts, s0);
   tmem_ld16(tp, d0);
@@ -96,7 +98,8 @@ __device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t 
     tmem_wait_ld_regs(s0, d0);
     tmem_ld16(ts + c0 + 16, s1);
     tmem_ld16(tp + c0 + 16, d1);
-    bwd_row_chunk<kFp16, kStoreA, false>(s0, d0, c0, c0, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
+    bwd_row_chunk<kFp16, kStoreA, kMasked>(s0, d0, c0, c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a,
+                                           tile_z);
     tmem_wait_ld_regs(s1, d1);
     if (pair < 3) {
       tmem_ld16(ts + c0 + 32, s0);
@@ -106,32 +109,9 @@ __device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t 
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar);
     }
-    bwd_row_chunk<kFp16, kStoreA, false>(s1, d1, c0 + 16, c0 + 16, r, false, 0, true, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
-    if (pair == 1 && mid_r1 != nullptr) {   // the carried values at key 64 of the tile
-      *mid_r1 = r1 + logsum;
-      *mid_s2 = gpre + gs;
-    }
-  }
-}
-
-template <bool kFp16, bool kStoreA>
-__device__ __forceinline__ void bwd_row_pass_masked(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r,
-                                                    bool diag, int ac, bool row_valid, float scale2, float r1, float gpre,
-                                                    float dr, float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z,
-                                                    float *mid_r1, float *mid_s2) {
-#pragma unroll 1
-  for (int ch = 0; ch < 8; ++ch) {
-    uint32_t s0[16], d0[16];
-    tmem_ld16(ts + ch * 16, s0);
-    tmem_ld16(tp + ch * 16, d0);
-    tmem_wait_ld_regs(s0, d0);
-    if (ch == 7) {
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar);
-    }
-    bwd_row_chunk<kFp16, kStoreA, true>(s0, d0, ch * 16, ch * 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a, tile_z);
-    if (ch == 3 && mid_r1 != nullptr) {
+    bwd_row_chunk<kFp16, kStoreA, kMasked>(s1, d1, c0 + 16, c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum,
+                                           tile_a, tile_z);
+    if (pair == 1 && mid_r1 != nullptr) {
       *mid_r1 = r1 + logsum;
       *mid_s2 = gpre + gs;
     }
@@ -280,11 +260,11 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       rec_s2[0] = gpre;
       float gs = 0.f, logsum = 0.f;
       if (j == I)
-        bwd_row_pass_masked<kFp16, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, true, p.attend_current, true,
-                                          scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
+        bwd_row_pass<kFp16, false, true>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, true, p.attend_current, true,
+                                         scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
       else
-        bwd_row_pass<kFp16, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, scale2, r1f, gpre, dr, gs, logsum,
-                                   nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
+        bwd_row_pass<kFp16, false, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, false, 0, true, scale2, r1f, gpre,
+                                          dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
       r1 += (double)logsum;
       gpre += gs;
       fence_proxy_async_smem();
@@ -452,11 +432,11 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       float gs = 0.f, logsum = 0.f;
       const bool diag = (i == 0);
       if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0))
-        bwd_row_pass_masked<kFp16, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, diag, p.attend_current, valid,
-                                         scale2, r1f, gpre, dr, gs, logsum, gA, gZ, nullptr, nullptr);
+        bwd_row_pass<kFp16, true, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, diag, p.attend_current, valid,
+                                        scale2, r1f, gpre, dr, gs, logsum, gA, gZ, nullptr, nullptr);
       else
-        bwd_row_pass<kFp16, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, scale2, r1f, gpre, dr, gs, logsum,
-                                  gA, gZ, nullptr, nullptr);
+        bwd_row_pass<kFp16, true, false>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, false, 0, true, scale2, r1f, gpre,
+                                         dr, gs, logsum, gA, gZ, nullptr, nullptr);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(vAzFull));
@@ -498,6 +478,33 @@ constexpr int kAzBytes = kBM * kBN * 2;        // A or dz tile, 128 rows x 64 ke
 constexpr int kSmem = 1024 + 2 * kStripBytes + 4 * kTileBytes + 4 * kAzBytes + 512;
 enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 9, bOutFull = 11, bNum = 12 };
 }  // namespace dkv2
+
+// One row of a 64-key strip: four 16-column chunks, TMEM read one chunk ahead.  mc0: key index of the strip's first
+// column inside its 128-key tile (for the diagonal mask).
+template <bool kFp16, bool kMasked>
+__device__ __forceinline__ void dkv2_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
+                                              float scale2, float r1, float gpre, float dr, float &gs, float &logsum,
+                                              uint8_t *tile_a, uint8_t *tile_z) {
+  uint32_t s0[16], d0[16], s1[16], d1[16];
+  tmem_ld16(ts, s0);
+  tmem_ld16(tp, d0);
+#pragma unroll 1
+  for (int pair = 0; pair < 2; ++pair) {
+    const int c0 = pair * 32;
+    tmem_wait_ld_regs(s0, d0);
+    tmem_ld16(ts + c0 + 16, s1);
+    tmem_ld16(tp + c0 + 16, d1);
+    bwd_row_chunk<kFp16, true, kMasked>(s0, d0, c0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a,
+                                        tile_z);
+    tmem_wait_ld_regs(s1, d1);
+    if (pair == 0) {
+      tmem_ld16(ts + 32, s0);
+      tmem_ld16(tp + 32, d0);
+    }
+    bwd_row_chunk<kFp16, true, kMasked>(s1, d1, c0 + 16, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs,
+                                        logsum, tile_a, tile_z);
+  }
+}
 
 template <bool kFp16>
 __global__ void __launch_bounds__(dkv2::kThreads, 1)
@@ -642,35 +649,10 @@ tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after();
       float gs = 0.f, logsum = 0.f;
       const bool diag = (i == 0);
-      if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0)) {
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t s0[16], d0[16];
-          tmem_ld16(tS + ch * 16, s0);
-          tmem_ld16(tP + ch * 16, d0);
-          tmem_wait_ld_regs(s0, d0);
-          bwd_row_chunk<kFp16, true, true>(s0, d0, ch * 16, half * kBN + ch * 16, r, diag, p.attend_current, valid, scale2,
-                                           r1f, gpre, dr, gs, logsum, gA, gZ);
-        }
-      } else {
-        uint32_t s0[16], d0[16], s1[16], d1[16];
-        tmem_ld16(tS, s0);
-        tmem_ld16(tP, d0);
-#pragma unroll 1
-        for (int pair = 0; pair < 2; ++pair) {
-          const int c0 = pair * 32;
-          tmem_wait_ld_regs(s0, d0);
-          tmem_ld16(tS + c0 + 16, s1);
-          tmem_ld16(tP + c0 + 16, d1);
-          bwd_row_chunk<kFp16, true, false>(s0, d0, c0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
-          tmem_wait_ld_regs(s1, d1);
-          if (pair == 0) {
-            tmem_ld16(tS + 32, s0);
-            tmem_ld16(tP + 32, d0);
-          }
-          bwd_row_chunk<kFp16, true, false>(s1, d1, c0 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
-        }
-      }
+      if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0))
+        dkv2_row_pass<kFp16, true>(tS, tP, r, half * kBN, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      else
+        dkv2_row_pass<kFp16, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
       tc_fence_before();          // this tile's TMEM reads are done before the slots are handed back
       fence_proxy_async_smem();
       __syncwarp();

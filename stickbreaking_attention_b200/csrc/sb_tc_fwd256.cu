@@ -63,6 +63,22 @@ __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0
   store_row_chunk16<kFp16>(tile_p, r, c0, pr);
 }
 
+template <bool kFp16, bool kMasked>
+__device__ __forceinline__ void fwd256_row_pass(uint32_t ts, int key0, int row, int ac, float scale2, float &R,
+                                                float &logsum, uint8_t *tile_p, int r) {
+  uint32_t va[16], vb[16];
+  tmem_ld16(ts + 48, va);
+#pragma unroll 1
+  for (int pair = 1; pair >= 0; --pair) {
+    tmem_wait_ld_regs(va);
+    tmem_ld16(ts + pair * 32, vb);
+    fwd256_row_chunk<kFp16, kMasked>(va, pair * 32 + 16, key0 + pair * 32 + 16, row, ac, scale2, R, logsum, tile_p, r);
+    tmem_wait_ld_regs(vb);
+    if (pair == 1) tmem_ld16(ts + 16, va);
+    fwd256_row_chunk<kFp16, kMasked>(vb, pair * 32, key0 + pair * 32, row, ac, scale2, R, logsum, tile_p, r);
+  }
+}
+
 template <bool kFp16>
 __global__ void __launch_bounds__(fwd256::kThreads, 1)
 tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -224,27 +240,8 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       float R = ex2(-(float)run);
       float logsum = 0.f;
       // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
-      if (s >= s_diag0) {
-#pragma unroll 1
-        for (int ch = 3; ch >= 0; --ch) {
-          uint32_t v[16];
-          tmem_ld16(ts + ch * 16, v);
-          tmem_wait_ld_regs(v);
-          fwd256_row_chunk<kFp16, true>(v, ch * 16, s * kBN + ch * 16, row, ac, scale2, R, logsum, tile_p, r);
-        }
-      } else {
-        uint32_t va[16], vb[16];
-        tmem_ld16(ts + 48, va);
-#pragma unroll 1
-        for (int pair = 1; pair >= 0; --pair) {
-          tmem_wait_ld_regs(va);
-          tmem_ld16(ts + pair * 32, vb);
-          fwd256_row_chunk<kFp16, false>(va, pair * 32 + 16, 0, 0, ac, scale2, R, logsum, tile_p, r);
-          tmem_wait_ld_regs(vb);
-          if (pair == 1) tmem_ld16(ts + 16, va);
-          fwd256_row_chunk<kFp16, false>(vb, pair * 32, 0, 0, ac, scale2, R, logsum, tile_p, r);
-        }
-      }
+      if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r);
+      else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r);
       run += (double)logsum;
       tc_fence_before();          // this step's TMEM reads are done before the slot is handed back
       fence_proxy_async_smem();
