@@ -481,8 +481,8 @@ enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 
 
 // One row of a 64-key strip: four 16-column chunks, TMEM read one chunk ahead.  mc0: key index of the strip's first
 // column inside its 128-key tile (for the diagonal mask).
-template <bool kFp16, bool kMasked>
-__device__ __forceinline__ void dkv2_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
+template <bool kFp16, bool kStoreA, bool kMasked>
+__device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
                                               float scale2, float r1, float gpre, float dr, float &gs, float &logsum,
                                               uint8_t *tile_a, uint8_t *tile_z) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
@@ -494,14 +494,14 @@ __device__ __forceinline__ void dkv2_row_pass(uint32_t ts, uint32_t tp, int r, i
     tmem_wait_ld_regs(s0, d0);
     tmem_ld16(ts + c0 + 16, s1);
     tmem_ld16(tp + c0 + 16, d1);
-    bwd_row_chunk<kFp16, true, kMasked>(s0, d0, c0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a,
+    bwd_row_chunk<kFp16, kStoreA, kMasked>(s0, d0, c0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a,
                                         tile_z);
     tmem_wait_ld_regs(s1, d1);
     if (pair == 0) {
       tmem_ld16(ts + 32, s0);
       tmem_ld16(tp + 32, d0);
     }
-    bwd_row_chunk<kFp16, true, kMasked>(s1, d1, c0 + 16, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs,
+    bwd_row_chunk<kFp16, kStoreA, kMasked>(s1, d1, c0 + 16, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs,
                                         logsum, tile_a, tile_z);
   }
 }
@@ -650,9 +650,9 @@ tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       float gs = 0.f, logsum = 0.f;
       const bool diag = (i == 0);
       if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0))
-        dkv2_row_pass<kFp16, true>(tS, tP, r, half * kBN, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+        strip_row_pass<kFp16, true, true>(tS, tP, r, half * kBN, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
       else
-        dkv2_row_pass<kFp16, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+        strip_row_pass<kFp16, true, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
       tc_fence_before();          // this tile's TMEM reads are done before the slots are handed back
       fence_proxy_async_smem();
       __syncwarp();
@@ -692,6 +692,202 @@ tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
+// =======================================================================================================
+// dq kernel for head sizes 72..128: 256 query rows per CTA
+// =======================================================================================================
+// Two adjacent 128-row query tiles (a, b) share one stream of 64-key K/V sub-tiles, walked from the sequence start
+// to tile b's diagonal.  Each tile has its own row-owning warpgroup (warps 0-3 / 4-7), MMA issuer (warps 9 / 10),
+// S/dP slots and dQ accumulator in TMEM and dz tile in shared memory.  Per sub-tile and tile: S = Q K^T and
+// dP = dO V^T (128 x 64), the row pass (which also records R1/S2 at the sub-tile's first key, i.e. at keys 0 and 64
+// of every 128-key tile), then dQ += dz K.
+// TMEM columns: S_a 0, dP_a 64, S_b 128, dP_b 192, dQ_a 256, dQ_b 384.
+namespace dq2 {
+constexpr int kThreads = 352;
+constexpr int kBN = 64;
+constexpr int kStages = 2;
+constexpr int kTileBytes = kBM * 128 * 2;      // Q or dO tile
+constexpr int kKvBox = kBN * 64 * 2;           // 64 keys x 64 columns
+constexpr int kKvTile = 2 * kKvBox;            // K or V sub-tile
+constexpr int kStageBytes = 2 * kKvTile;
+constexpr int kZBytes = kBM * kBN * 2;         // dz tile: 128 rows x 64 keys
+constexpr int kSmem = 1024 + 4 * kTileBytes + kStages * kStageBytes + 2 * kZBytes + 512;
+enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bDqFull = 11, bNum = 12 };
+}  // namespace dq2
+
+template <bool kFp16>
+__global__ void __launch_bounds__(dq2::kThreads, 1)
+tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
+  using namespace dq2;
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x, true, c)) return;
+  if (c.idx & 1) return;                        // the block of tiles (idx, idx + 1) belongs to the even tile's CTA
+  const int Ia = c.idx;
+  const bool b_active = Ia + 1 < c.n_tiles;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  const uint32_t sQ = base;                     // tile w: Q at sQ + w * 2 * kTileBytes, dO right behind it
+  const uint32_t sKV = sQ + 4 * kTileBytes;     // stage: K sub-tile then V sub-tile
+  const uint32_t sZ = sKV + kStages * kStageBytes;
+  const uint32_t sBar = sZ + 2 * kZBytes;
+  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
+  volatile int *abort_flag = &ctl->abort;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int n_sub = (c.len + kBN - 1) / kBN;
+  const int steps_a = min(2 * Ia + 2, n_sub);            // sub-tiles 0 .. 2 Ia + 1 reach tile a's diagonal
+  const int steps_b = b_active ? min(2 * Ia + 4, n_sub) : 0;
+  const int n_steps = b_active ? steps_b : steps_a;
+  const int issuers = b_active ? 2 : 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(bQG), 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar(bKvFull + s), 1); mbar_init(bar(bKvEmpty + s), issuers); }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(bar(bSpFull + w), 1);
+      mbar_init(bar(bZFull + w), 4);
+      mbar_init(bar(bZEmpty + w), 1);
+    }
+    mbar_init(bar(bDqFull), issuers);
+    ctl->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
+      const int qrow = (int)c.tok0 + Ia * kBM;
+      mbar_arrive_expect_tx(bar(bQG), 4 * kTileBytes);
+      for (int w = 0; w < 2; ++w)
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(sQ + w * 2 * kTileBytes + kb * kBoxBytes, &tm_q, bar(bQG), kb * 64, qrow + w * kBM, h, (int)c.boff);
+          tma_load_4d(sQ + w * 2 * kTileBytes + kTileBytes + kb * kBoxBytes, &tm_g, bar(bQG), kb * 64, qrow + w * kBM, h, (int)c.boff);
+        }
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t % kStages;
+        if (t >= kStages && !wait_or_abort(bar(bKvEmpty + st), ((t / kStages) - 1) & 1, abort_flag, p, 510)) break;
+        if (*abort_flag) break;
+        const int krow = (int)c.tok0 + t * kBN;
+        const uint32_t dst = sKV + st * kStageBytes;
+        mbar_arrive_expect_tx(bar(bKvFull + st), kStageBytes);
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(dst + kb * kKvBox, &tm_k, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
+          tma_load_4d(dst + kKvTile + kb * kKvBox, &tm_v, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
+        }
+      }
+    }
+  } else if (warp >= 9) {
+    // ------------------------------------------------ MMA issuers, one per tile
+    const int w = warp - 9;
+    if (lane == 0 && w < issuers) {
+      constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);
+      constexpr uint32_t idesc_dq = idesc_f16(kBM, D, kFp16, false, true);
+      const uint32_t qaddr = sQ + w * 2 * kTileBytes, gaddr = qaddr + kTileBytes, zaddr = sZ + w * kZBytes;
+      const uint32_t tS = tmem + w * 128, tP = tS + 64, tDQ = tmem + 256 + w * 128;
+      const int my_steps = w == 0 ? steps_a : steps_b;
+      auto issue_sp = [&](int t) {
+        const uint32_t kaddr = sKV + (t % kStages) * kStageBytes;
+        mma_kmajor_kmajor<D, kBoxBytes, kKvBox>(tS, qaddr, kaddr, idesc_s, false);            // S = Q K^T
+        mma_kmajor_kmajor<D, kBoxBytes, kKvBox>(tP, gaddr, kaddr + kKvTile, idesc_s, false);  // dP = dO V^T
+        mma_commit(bar(bSpFull + w));
+      };
+      bool ok = wait_or_abort(bar(bQG), 0, abort_flag, p, 520) && wait_or_abort(bar(bKvFull), 0, abort_flag, p, 521);
+      // tile b starts once tile a's first scores are done, so that one tile's MMAs fall into the other's row pass
+      if (ok && w == 1 && steps_a > 0) ok = wait_or_abort(bar(bSpFull + 0), 0, abort_flag, p, 525);
+      if (ok) { tc_fence_after(); issue_sp(0); }
+      for (int u = 0; ok && u < my_steps; ++u) {
+        // the rows of step u are done (their S/dP reads too): next scores first, then this step's dQ
+        ok = wait_or_abort(bar(bZFull + w), u & 1, abort_flag, p, 522);
+        if (!ok) break;
+        if (u + 1 < my_steps) {
+          ok = wait_or_abort(bar(bKvFull + (u + 1) % kStages), ((u + 1) / kStages) & 1, abort_flag, p, 523);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sp(u + 1);
+        } else {
+          tc_fence_after();
+        }
+        // dQ += dz K: dz [128 x 64] K-major, K sub-tile [64 keys x (2 x 64) columns] MN-major
+        mma_kmajor_mnmajor<kBN, kKvBox>(tDQ, zaddr, sKV + (u % kStages) * kStageBytes, idesc_dq, u > 0);
+        mma_commit(bar(bZEmpty + w));
+        mma_commit(bar(bKvEmpty + u % kStages));
+      }
+      // tile a does not read the last sub-tiles: release them on its behalf once they have arrived
+      for (int t = my_steps; ok && t < n_steps; ++t) {
+        ok = wait_or_abort(bar(bKvFull + t % kStages), (t / kStages) & 1, abort_flag, p, 524);
+        if (ok) mbar_arrive(bar(bKvEmpty + t % kStages));
+      }
+      if (ok) mma_commit(bar(bDqFull));
+    }
+  } else {
+    // ------------------------------------------------ rows: warpgroup w owns query tile Ia + w
+    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
+    const int w = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const float scale2 = p.scale * kLog2e;
+    const int I = Ia + w;
+    const int my_steps = w == 0 ? steps_a : steps_b;
+    const int gi = I * kBM + r;
+    const bool valid = gi < c.len;
+    const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + gi;
+    double r1 = (valid && my_steps > 0) ? p.log_rem[idx] : 0.0;   // sum of log2(1-beta) over the keys from the current one on
+    const float dr = (valid && my_steps > 0) ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]) : 0.f;
+    float gpre = 0.f;
+    uint8_t *gZ = gbase + (sZ - base) + w * kZBytes;
+    const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
+    // boundary records: [pair (I, J)][half][row]; sub-tile u is half u & 1 of key tile u >> 1
+    const long long rec0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (2 * kBM) + r;
+    bool ok = true;
+    for (int u = 0; u < my_steps && ok; ++u) {
+      ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 530);
+      if (ok && u >= 1) ok = wait_or_abort(bar(bZEmpty + w), (u - 1) & 1, abort_flag, p, 531);
+      if (!ok) break;
+      tc_fence_after();
+      const float r1f = (float)r1;
+      p.bnd_r1[rec0 + (long long)u * kBM] = r1f;
+      p.bnd_s2[rec0 + (long long)u * kBM] = gpre;
+      float gs = 0.f, logsum = 0.f;
+      if (u >= 2 * I)
+        strip_row_pass<kFp16, false, true>(tS, tP, r, (u - 2 * I) * kBN, true, p.attend_current, true, scale2, r1f, gpre, dr,
+                                           gs, logsum, nullptr, gZ);
+      else
+        strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ);
+      r1 += (double)logsum;
+      gpre += gs;
+      tc_fence_before();          // this step's TMEM reads are done before the slots are handed back
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bZFull + w));
+    }
+    if (ok && my_steps > 0) ok = wait_or_abort(bar(bDqFull), 0, abort_flag, p, 532);
+    if (ok && my_steps > 0) {
+      tc_fence_after();
+      T *grow = reinterpret_cast<T *>(p.dq.ptr) + c.boff * p.dq.sb + (long long)h * p.dq.sh + (c.tok0 + gi) * p.dq.st;
+      store_acc_rows<D, kFp16, T>(tmem + 256 + w * 128 + lane_off, grow, valid, p.head_dim, p.scale);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+}
+
 // -------------------------------------------------------------------------------------------------------
 template <int D, bool kFp16>
 static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
@@ -702,7 +898,18 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
   if ((e = make_tile_map(&mv, p.v, p, dtype)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mg, p.d_o, p, dtype)) != cudaSuccess) return e;
   dim3 grid(p.tiles_cap, p.head_cnt);
-  if (!p.skip_dq) {
+  CUtensorMap mk64, mv64;   // 64-row boxes for the kernels that stream 64-key sub-tiles
+  if (D == 128) {
+    if ((e = make_tile_map(&mk64, p.k, p, dtype, 64)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mv64, p.v, p, dtype, 64)) != cudaSuccess) return e;
+  }
+  if (!p.skip_dq && D == 128) {
+    auto kernel = tc_bwd_dq2_kernel<kFp16>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq2::kSmem);
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, p);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  } else if (!p.skip_dq) {
     auto kernel = tc_bwd_dq_kernel<D, kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::kSmem);
     if (e != cudaSuccess) return e;
@@ -710,9 +917,6 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   if (!p.skip_dkv && D == 128) {
-    CUtensorMap mk64, mv64;
-    if ((e = make_tile_map(&mk64, p.k, p, dtype, dkv2::kBN)) != cudaSuccess) return e;
-    if ((e = make_tile_map(&mv64, p.v, p, dtype, dkv2::kBN)) != cudaSuccess) return e;
     auto kernel = tc_bwd_dkv2_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv2::kSmem);
     if (e != cudaSuccess) return e;
