@@ -31,31 +31,32 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
                                               float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
   // columns (tile-local key indices) below `limit` are allowed: one compare per column, no branches
   const int limit = !row_valid ? -1 : (diag ? r + ac : 0x7fffffff);
+  const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
   float be[16], ri[16];
 #pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    float e[4], t[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      e[i] = ex2(fminf(__uint_as_float(s[4 * g + i]) * scale2, 30.f));
-      t[i] = 1.f + e[i];
-      if (kMasked) {
-        const bool allowed = mc0 + 4 * g + i < limit;   // mc0: key index inside the 128-key tile (c0 addresses the output)
-        e[i] = allowed ? e[i] : 0.f;
-        t[i] = allowed ? t[i] : 1.f;
-      }
+  for (int g = 0; g < 4; ++g) {   // independent work in packed pairs (two fp32 per instruction)
+    const float2 x01 = mul2(make_float2(__uint_as_float(s[4 * g]), __uint_as_float(s[4 * g + 1])), sc);
+    const float2 x23 = mul2(make_float2(__uint_as_float(s[4 * g + 2]), __uint_as_float(s[4 * g + 3])), sc);
+    float2 e01 = make_float2(ex2(fminf(x01.x, 30.f)), ex2(fminf(x01.y, 30.f)));
+    float2 e23 = make_float2(ex2(fminf(x23.x, 30.f)), ex2(fminf(x23.y, 30.f)));
+    float2 t01 = add2(e01, one), t23 = add2(e23, one);
+    if (kMasked) {
+      const int col = mc0 + 4 * g;   // mc0: key index inside the 128-key tile (c0 only addresses the output tile)
+      if (!(col < limit)) { e01.x = 0.f; t01.x = 1.f; }
+      if (!(col + 1 < limit)) { e01.y = 0.f; t01.y = 1.f; }
+      if (!(col + 2 < limit)) { e23.x = 0.f; t23.x = 1.f; }
+      if (!(col + 3 < limit)) { e23.y = 0.f; t23.y = 1.f; }
     }
-    const float p01 = t[0] * t[1], p23 = t[2] * t[3];
-    const float prod = p01 * p23;
+    const float2 pp = mul2(make_float2(t01.x, t23.x), make_float2(t01.y, t23.y));   // (t0 t1, t2 t3)
+    const float prod = pp.x * pp.y;
     const float rp = rcp(prod);
     logsum += lg2(prod);
-    const float a = rp * p23, b = rp * p01;
-    ri[4 * g + 0] = a * t[1];
-    ri[4 * g + 1] = a * t[0];
-    ri[4 * g + 2] = b * t[3];
-    ri[4 * g + 3] = b * t[2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) be[4 * g + i] = e[i] * ri[4 * g + i];
+    const float2 ab = mul2(make_float2(rp, rp), make_float2(pp.y, pp.x));           // (rp t2 t3, rp t0 t1)
+    const float2 ri01 = mul2(make_float2(ab.x, ab.x), make_float2(t01.y, t01.x));   // (1/t0, 1/t1)
+    const float2 ri23 = mul2(make_float2(ab.y, ab.y), make_float2(t23.y, t23.x));   // (1/t2, 1/t3)
+    const float2 be01 = mul2(e01, ri01), be23 = mul2(e23, ri23);
+    ri[4 * g + 0] = ri01.x; ri[4 * g + 1] = ri01.y; ri[4 * g + 2] = ri23.x; ri[4 * g + 3] = ri23.y;
+    be[4 * g + 0] = be01.x; be[4 * g + 1] = be01.y; be[4 * g + 2] = be23.x; be[4 * g + 3] = be23.y;
   }
   float W = ex2(r1 + logsum);
   float pa[16];
@@ -65,17 +66,24 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
     W *= ri[i];
   }
   float pz[16];
+  const float2 ndr = make_float2(-dr, -dr), gp = make_float2(gpre, gpre);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    float g = pa[i] * (__uint_as_float(dp[i]) - dr);
+  for (int i = 0; i < 16; i += 2) {
+    float2 g2 = mul2(make_float2(pa[i], pa[i + 1]),
+                     add2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ndr));
     if (kMasked) {   // rows past the sequence end carry arbitrary values: select, do not rely on 0 * x
-      const bool allowed = mc0 + i < limit;
-      g = allowed ? g : 0.f;
-      pa[i] = allowed ? pa[i] : 0.f;
+      if (!(mc0 + i < limit)) { g2.x = 0.f; pa[i] = 0.f; }
+      if (!(mc0 + i + 1 < limit)) { g2.y = 0.f; pa[i + 1] = 0.f; }
     }
-    gs += g;
-    pz[i] = fmaf(-be[i], gpre + gs, g);
-    if (kMasked) pz[i] = row_valid ? pz[i] : 0.f;
+    const float gs0 = gs + g2.x;
+    gs = gs0 + g2.y;
+    const float2 z2 = fma2(make_float2(-be[i], -be[i + 1]), add2(make_float2(gs0, gs), gp), g2);
+    pz[i] = z2.x;
+    pz[i + 1] = z2.y;
+    if (kMasked) {
+      pz[i] = row_valid ? pz[i] : 0.f;
+      pz[i + 1] = row_valid ? pz[i + 1] : 0.f;
+    }
   }
   if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
   store_row_chunk16<kFp16>(tile_z, r, c0, pz);

@@ -35,30 +35,40 @@ template <bool kFp16, bool kMasked>
 __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0, int key0, int row, int ac,
                                                  float scale2, float &R, float &logsum, uint8_t *tile_p, int r) {
   float pr[16];
+  const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
 #pragma unroll
-  for (int g = 3; g >= 0; --g) {   // four columns at a time, last group first
-    float e[4], t[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      e[i] = ex2(fminf(__uint_as_float(v[4 * g + i]) * scale2, 30.f));
-      t[i] = 1.f + e[i];
-      if (kMasked) {
-        const bool allowed = key0 + 4 * g + i < row + ac;
-        e[i] = allowed ? e[i] : 0.f;
-        t[i] = allowed ? t[i] : 1.f;
-      }
+  for (int g = 3; g >= 0; --g) {   // four columns at a time, last group first; independent work in packed pairs
+    const float2 x01 = mul2(make_float2(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1])), sc);
+    const float2 x23 = mul2(make_float2(__uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3])), sc);
+    float2 e01 = make_float2(ex2(fminf(x01.x, 30.f)), ex2(fminf(x01.y, 30.f)));
+    float2 e23 = make_float2(ex2(fminf(x23.x, 30.f)), ex2(fminf(x23.y, 30.f)));
+    float2 t01 = add2(e01, one), t23 = add2(e23, one);
+    if (kMasked) {
+      const int key = key0 + 4 * g, lim = row + ac;
+      if (!(key < lim)) { e01.x = 0.f; t01.x = 1.f; }
+      if (!(key + 1 < lim)) { e01.y = 0.f; t01.y = 1.f; }
+      if (!(key + 2 < lim)) { e23.x = 0.f; t23.x = 1.f; }
+      if (!(key + 3 < lim)) { e23.y = 0.f; t23.y = 1.f; }
     }
     // one reciprocal and one logarithm for the four factors (1 + e): 1/t_i = (1 / t0 t1 t2 t3) * (product of the others)
-    const float p01 = t[0] * t[1], p23 = t[2] * t[3];
-    const float prod = p01 * p23;
+    const float2 pp = mul2(make_float2(t01.x, t23.x), make_float2(t01.y, t23.y));   // (t0 t1, t2 t3)
+    const float prod = pp.x * pp.y;
     const float rp = rcp(prod);
     logsum += lg2(prod);
-    const float a = rp * p23, b = rp * p01;
-    const float ri3 = b * t[2], ri2 = b * t[3], ri1 = a * t[0], ri0 = a * t[1];
-    pr[4 * g + 3] = (e[3] * ri3) * R; R *= ri3;
-    pr[4 * g + 2] = (e[2] * ri2) * R; R *= ri2;
-    pr[4 * g + 1] = (e[1] * ri1) * R; R *= ri1;
-    pr[4 * g + 0] = (e[0] * ri0) * R; R *= ri0;
+    const float2 ab = mul2(make_float2(rp, rp), make_float2(pp.y, pp.x));           // (rp t2 t3, rp t0 t1)
+    const float2 ri01 = mul2(make_float2(ab.x, ab.x), make_float2(t01.y, t01.x));   // (1/t0, 1/t1)
+    const float2 ri23 = mul2(make_float2(ab.y, ab.y), make_float2(t23.y, t23.x));   // (1/t2, 1/t3)
+    const float2 be01 = mul2(e01, ri01), be23 = mul2(e23, ri23);
+    // R after columns 3, 3..2, 3..1 of the group; after all four it is R * rp
+    const float r3 = R * ri23.y;
+    const float2 r21 = mul2(make_float2(r3, r3), make_float2(ri23.x, ri23.x * ri01.y));
+    const float2 p32 = mul2(make_float2(be23.y, be23.x), make_float2(R, r3));
+    const float2 p10 = mul2(make_float2(be01.y, be01.x), r21);
+    pr[4 * g + 3] = p32.x;
+    pr[4 * g + 2] = p32.y;
+    pr[4 * g + 1] = p10.x;
+    pr[4 * g + 0] = p10.y;
+    R *= rp;
   }
   store_row_chunk16<kFp16>(tile_p, r, c0, pr);
 }
