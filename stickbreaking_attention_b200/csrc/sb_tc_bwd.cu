@@ -641,15 +641,23 @@ tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint8_t *gZ = gA + kAzBytes;
     const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
     bool ok = true;
+    // the per-row start values of a tile come from global memory: they are fetched one tile ahead
+    auto fetch = [&](int i, float &r1f, float &gpre, float &dr) {
+      const int I = J + i;
+      const int gi = I * kBM + r;
+      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 2 + half) * kBM + r;
+      r1f = p.bnd_r1[slot];
+      gpre = p.bnd_s2[slot];
+      dr = gi < c.len ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
+    };
+    float nr1 = 0.f, ngpre = 0.f, ndr = 0.f;
+    if (w < cnt) fetch(w, nr1, ngpre, ndr);
     for (int i = w, u = 0; i < cnt && ok; i += 2, ++u) {
       const int I = J + i;
       const int gi = I * kBM + r;
       const bool valid = gi < c.len;
-      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 2 + half) * kBM + r;
-      const float r1f = p.bnd_r1[slot];
-      const float gpre = p.bnd_s2[slot];
-      const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(
-                                   p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
+      const float r1f = nr1, gpre = ngpre, dr = ndr;
+      if (i + 2 < cnt) fetch(i + 2, nr1, ngpre, ndr);
       ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 430);
       if (ok && u >= 1) ok = wait_or_abort(bar(bAzEmpty + w), (u - 1) & 1, abort_flag, p, 431);
       if (!ok) break;
