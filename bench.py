@@ -40,6 +40,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
+# profiles/tc_kernels_c2_ncu.md (workload c2 only; other workloads report null)
+NCU_TRAFFIC_BYTES = {"c2": {"fwd": 250.1e6, "bwd_dq": 354.9e6, "bwd_dkv": 416.7e6}}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -350,7 +353,8 @@ def run_gpu_arm(args, w):
         top = max(kern, key=lambda n: kern[n])
         achieved = kernels[top]["tflops"]
         roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_tflops"],
-                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "traffic": NCU_TRAFFIC_BYTES.get(args.workload, {}).get(top),
                     "peak_source": f"{peak_kind} dense bf16 (burst)", "kernels": kernels,
                     "step_frac_of_peak": value / world / peaks["bf16_tflops"],
                     "kernel_path": "tcgen05" if path == 1 else "cuda-core"}
