@@ -148,6 +148,10 @@ def cpu_sample(w, heads, seqs, reps):
     """Times forward+backward of the oracle on `heads` heads x the first `seqs` sequences; returns
     (best seconds, TFLOP/s under the causal convention, description)."""
     from oracle import sb_oracle as O
+    try:   # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        pass
     lengths = w["lengths"][:seqs]
     gen = torch.Generator().manual_seed(0)
     shape = (heads, sum(lengths), w["head_dim"])
@@ -171,8 +175,9 @@ def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = torch.get_num_threads()
     heads, seqs = min(4, w["heads"]), 1
+    cpu_sample(w, 1, 1, 1)            # sets the thread count; also warms the allocator
+    threads = torch.get_num_threads()
     times = []
     tfl = 0.0
     desc = ""
