@@ -168,10 +168,6 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tma_load_4d(dst + kb * kKvBoxBytes, &tm_k, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
           tma_load_4d(dst + kKvTileBytes + kb * kKvBoxBytes, &tm_v, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
         }
-        if (p.dbg == 9) {   // experiment: measure the load latency directly
-          while (!mbar_try_wait(bar(bKvFull + st), (t / kStages) & 1)) {}
-          trace_event(p, 0, tr_cur, 8, t);
-        }
       }
     }
   } else if (warp >= 9) {
@@ -241,12 +237,6 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_after();
       const uint32_t ts = tmem + wg * 128 + buf * 64 + lane_off;
       uint8_t *tile_p = gP + (wg * 2 + buf) * kPBytes;
-      if (p.dbg == 5) {   // experiment: no row work at all, only the barrier protocol
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(bPFull + wg * 2 + buf));
-        continue;
-      }
       float R = ex2(-(float)run);
       float logsum = 0.f;
       // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
