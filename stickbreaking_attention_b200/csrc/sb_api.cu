@@ -93,8 +93,8 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   pl.off_tile_prefix = 256;
   pl.off_pair_prefix = align_up(pl.off_tile_prefix + sizeof(int) * (size_t)(p->num_seq + 1), 256);
   pl.off_bnd = align_up(pl.off_pair_prefix + sizeof(long long) * (size_t)(p->num_seq + 1), 256);
-  // the tensor-core path records the carried values twice per 128-key tile (at keys 0 and 64)
-  pl.bnd_halves = tc ? 2 : 1;
+  // the tensor-core path records the carried values four times per 128-key tile
+  pl.bnd_halves = tc ? 4 : 1;   // keys 0, 32, 64, 96 of every 128-key tile
   pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * pl.bnd_halves * sizeof(float), 256);
   size_t chunk = pl.bnd_bytes_per_head ? kBoundaryBudget / (2 * pl.bnd_bytes_per_head) : (size_t)p->heads;
   if (chunk < 1) chunk = 1;

@@ -254,7 +254,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]) : 0.f;
     float gpre = 0.f;
     // boundary records: [pair][half: keys 0.. / keys 64..][row]
-    const long long slot0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (2 * kBM) + r;
+    const long long slot0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (4 * kBM) + r;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       ok = wait_or_abort(bar(qSpFull), j & 1, abort_flag, p, 130);
@@ -262,17 +262,17 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const float r1f = (float)r1;
-      float *rec_r1 = p.bnd_r1 + slot0 + (long long)j * (2 * kBM);
-      float *rec_s2 = p.bnd_s2 + slot0 + (long long)j * (2 * kBM);
+      float *rec_r1 = p.bnd_r1 + slot0 + (long long)j * (4 * kBM);
+      float *rec_s2 = p.bnd_s2 + slot0 + (long long)j * (4 * kBM);
       rec_r1[0] = r1f;
       rec_s2[0] = gpre;
       float gs = 0.f, logsum = 0.f;
       if (j == I)
         bwd_row_pass<kFp16, false, true>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, true, p.attend_current, true,
-                                         scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
+                                         scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, rec_r1 + 2 * kBM, rec_s2 + 2 * kBM);
       else
         bwd_row_pass<kFp16, false, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, false, 0, true, scale2, r1f, gpre,
-                                          dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
+                                          dr, gs, logsum, nullptr, gZ, rec_r1 + 2 * kBM, rec_s2 + 2 * kBM);
       r1 += (double)logsum;
       gpre += gs;
       fence_proxy_async_smem();
@@ -428,7 +428,7 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int I = J + i;
       const int gi = I * kBM + r;
       const bool valid = gi < c.len;
-      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * (2 * kBM) + r;
+      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * (4 * kBM) + r;
       const float r1f = p.bnd_r1[slot];
       const float gpre = p.bnd_s2[slot];
       const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(
@@ -492,7 +492,8 @@ enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 
 template <bool kFp16, bool kStoreA, bool kMasked>
 __device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
                                               float scale2, float r1, float gpre, float dr, float &gs, float &logsum,
-                                              uint8_t *tile_a, uint8_t *tile_z) {
+                                              uint8_t *tile_a, uint8_t *tile_z, float *mid_r1 = nullptr,
+                                              float *mid_s2 = nullptr) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
   tmem_ld16(ts, s0);
   tmem_ld16(tp, d0);
@@ -511,6 +512,10 @@ __device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, 
     }
     bwd_row_chunk<kFp16, kStoreA, kMasked>(s1, d1, c0 + 16, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs,
                                         logsum, tile_a, tile_z);
+    if (pair == 0 && mid_r1 != nullptr) {   // the carried values after 32 of the 64 columns
+      *mid_r1 = r1 + logsum;
+      *mid_s2 = gpre + gs;
+    }
   }
 }
 
@@ -645,7 +650,7 @@ tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     auto fetch = [&](int i, float &r1f, float &gpre, float &dr) {
       const int I = J + i;
       const int gi = I * kBM + r;
-      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 2 + half) * kBM + r;
+      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 4 + 2 * half) * kBM + r;
       r1f = p.bnd_r1[slot];
       gpre = p.bnd_s2[slot];
       dr = gi < c.len ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
@@ -868,7 +873,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint8_t *gZ = gbase + (sZ - base) + w * kZBytes;
     const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
     // boundary records: [pair (I, J)][half][row]; sub-tile u is half u & 1 of key tile u >> 1
-    const long long rec0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (2 * kBM) + r;
+    const long long rec0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (4 * kBM) + r;
     bool ok = true;
     for (int u = 0; u < my_steps && ok; ++u) {
       ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 530);
@@ -876,14 +881,17 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       const float r1f = (float)r1;
-      p.bnd_r1[rec0 + (long long)u * kBM] = r1f;
-      p.bnd_s2[rec0 + (long long)u * kBM] = gpre;
+      float *rec_r1 = p.bnd_r1 + rec0 + (long long)u * (2 * kBM);   // quarter 2 (u & 1) of key tile u >> 1
+      float *rec_s2 = p.bnd_s2 + rec0 + (long long)u * (2 * kBM);
+      rec_r1[0] = r1f;
+      rec_s2[0] = gpre;
       float gs = 0.f, logsum = 0.f;
       if (u >= 2 * I)
         strip_row_pass<kFp16, false, true>(tS, tP, r, (u - 2 * I) * kBN, true, p.attend_current, true, scale2, r1f, gpre, dr,
-                                           gs, logsum, nullptr, gZ);
+                                           gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
       else
-        strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ);
+        strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
+                                            rec_r1 + kBM, rec_s2 + kBM);
       r1 += (double)logsum;
       gpre += gs;
       tc_fence_before();          // this step's TMEM reads are done before the slots are handed back
@@ -896,6 +904,229 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after();
       T *grow = reinterpret_cast<T *>(p.dq.ptr) + c.boff * p.dq.sb + (long long)h * p.dq.sh + (c.tok0 + gi) * p.dq.st;
       store_acc_rows<D, kFp16, T>(tmem + 256 + w * 128 + lane_off, grow, valid, p.head_dim, p.scale);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+}
+
+// =======================================================================================================
+// dkv kernel for head sizes 72..128, pipelined: one CTA per 64-key strip, all eight row warps on one query tile
+// =======================================================================================================
+// Warps 0-3 own key columns 0..31 of the strip and warps 4-7 columns 32..63 for the same 128 query rows; each half
+// restarts from its own R1/S2 record (the dq kernel records them every 32 keys), so the halves are independent.
+// With S/dP and the A/dz tiles double-buffered and the Q/dO tiles in a two-stage ring, the S/dP MMAs of tile u+1
+// (issuer warp 9) and the dK^T/dV^T MMAs of tile u-1 (issuer warp 10) run while the rows of tile u are processed.
+// TMEM columns: S[b] at 128 b, dP[b] at 128 b + 64, dK^T 256, dV^T 320.
+namespace dkv3 {
+constexpr int kThreads = 352;
+constexpr int kBN = 64;
+constexpr int kTileBytes = kBM * 128 * 2;      // Q or dO tile
+constexpr int kStripBytes = kBN * 128 * 2;     // K or V strip: two 64x64 boxes
+constexpr int kStripBox = kBN * 64 * 2;
+constexpr int kAzBytes = kBM * kBN * 2;        // A or dz tile, 128 rows x 64 keys
+constexpr int kSmem = 1024 + 2 * kStripBytes + 4 * kTileBytes + 4 * kAzBytes + 512;
+enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 9, bOutFull = 11, bNum = 12 };
+}  // namespace dkv3
+
+template <bool kFp16>
+__global__ void __launch_bounds__(dkv3::kThreads, 1)
+tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
+  using namespace dkv3;
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  if (!decode_tile(p, blockIdx.x >> 1, false, c)) return;
+  const int half = blockIdx.x & 1;
+  const int J = c.idx;                         // 128-key tile of the strip
+  const int key0 = J * kBM + half * kBN;       // first key of the strip inside the sequence
+  if (key0 >= c.len) return;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  const uint32_t sK = base;
+  const uint32_t sV = sK + kStripBytes;
+  const uint32_t sQ = sV + kStripBytes;              // stage b: Q at sQ + b * 2 * kTileBytes, dO right behind it
+  const uint32_t sAZ = sQ + 4 * kTileBytes;          // buffer b: A at sAZ + b * 2 * kAzBytes, dz right behind it
+  const uint32_t sBar = sAZ + 4 * kAzBytes;
+  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
+  volatile int *abort_flag = &ctl->abort;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int cnt = c.n_tiles - J;               // query tiles J .. n_tiles-1
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(bKV), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(bQgFull + b), 1);
+      mbar_init(bar(bQgEmpty + b), 1);
+      mbar_init(bar(bSpFull + b), 1);
+      mbar_init(bar(bAzFull + b), 8);
+      mbar_init(bar(bAzEmpty + b), 1);
+    }
+    mbar_init(bar(bOutFull), 1);
+    ctl->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
+      const int krow = (int)c.tok0 + key0;
+      mbar_arrive_expect_tx(bar(bKV), 2 * kStripBytes);
+      for (int kb = 0; kb < 2; ++kb) {
+        tma_load_4d(sK + kb * kStripBox, &tm_k, bar(bKV), kb * 64, krow, h, (int)c.boff);
+        tma_load_4d(sV + kb * kStripBox, &tm_v, bar(bKV), kb * 64, krow, h, (int)c.boff);
+      }
+      for (int u = 0; u < cnt; ++u) {
+        const int b = u & 1;
+        if (u >= 2 && !wait_or_abort(bar(bQgEmpty + b), ((u >> 1) - 1) & 1, abort_flag, p, 610)) break;
+        if (*abort_flag) break;
+        const int qrow = (int)c.tok0 + (J + u) * kBM;
+        const uint32_t dst = sQ + b * 2 * kTileBytes;
+        mbar_arrive_expect_tx(bar(bQgFull + b), 2 * kTileBytes);
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(dst + kb * kBoxBytes, &tm_q, bar(bQgFull + b), kb * 64, qrow, h, (int)c.boff);
+          tma_load_4d(dst + kTileBytes + kb * kBoxBytes, &tm_g, bar(bQgFull + b), kb * 64, qrow, h, (int)c.boff);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------ issuer of S = Q K^T and dP = dO V^T (128 x 64)
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);
+      bool ok = wait_or_abort(bar(bKV), 0, abort_flag, p, 620);
+      for (int u = 0; ok && u < cnt; ++u) {
+        const int b = u & 1;
+        ok = wait_or_abort(bar(bQgFull + b), (u >> 1) & 1, abort_flag, p, 621);
+        // the rows of tile u-2 have left this S/dP buffer once its A/dz tiles were signalled
+        if (ok && u >= 2) ok = wait_or_abort(bar(bAzFull + b), ((u >> 1) - 1) & 1, abort_flag, p, 622);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t qaddr = sQ + b * 2 * kTileBytes;
+        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tmem + b * 128, qaddr, sK, idesc_s, false);
+        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tmem + b * 128 + 64, qaddr + kTileBytes, sV, idesc_s, false);
+        mma_commit(bar(bSpFull + b));
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------ issuer of dK^T += Q^T dz and dV^T += dO^T A (128 x 64)
+    if (lane == 0) {
+      constexpr uint32_t idesc_t = idesc_f16(kBM, kBN, kFp16, true, true);
+      bool ok = true;
+      for (int u = 0; ok && u < cnt; ++u) {
+        const int b = u & 1;
+        ok = wait_or_abort(bar(bAzFull + b), (u >> 1) & 1, abort_flag, p, 623);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t qaddr = sQ + b * 2 * kTileBytes, aaddr = sAZ + b * 2 * kAzBytes;
+        const uint64_t q0 = smem_desc_sw128(qaddr, kBoxBytes, 1024), g0 = smem_desc_sw128(qaddr + kTileBytes, kBoxBytes, 1024);
+        const uint64_t a0 = smem_desc_sw128(aaddr, 16, 1024), z0 = smem_desc_sw128(aaddr + kAzBytes, 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < kBM / 16; ++ks)
+          mma_f16_ss(tmem + 256, q0 + (uint64_t)(ks * 128), z0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < kBM / 16; ++ks)
+          mma_f16_ss(tmem + 320, g0 + (uint64_t)(ks * 128), a0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
+        mma_commit(bar(bQgEmpty + b));
+        mma_commit(bar(bAzEmpty + b));
+      }
+      if (ok) mma_commit(bar(bOutFull));
+    }
+  } else {
+    // ------------------------------------------------ rows: warps 0-3 columns 0..31, warps 4-7 columns 32..63
+    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
+    const int w = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const float scale2 = p.scale * kLog2e;
+    const int quarter = 2 * half + w;            // which 32-key quarter of the 128-key tile
+    bool ok = true;
+    // the per-row start values of a tile come from global memory: they are fetched one tile ahead
+    auto fetch = [&](int u, float &r1f, float &gpre, float &dr) {
+      const int I = J + u;
+      const int gi = I * kBM + r;
+      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 4 + quarter) * kBM + r;
+      r1f = p.bnd_r1[slot];
+      gpre = p.bnd_s2[slot];
+      dr = gi < c.len ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
+    };
+    float nr1, ngpre, ndr;
+    fetch(0, nr1, ngpre, ndr);
+    for (int u = 0; u < cnt && ok; ++u) {
+      const int b = u & 1;
+      const int I = J + u;
+      const bool valid = I * kBM + r < c.len;
+      const float r1f = nr1, gpre = ngpre, dr = ndr;
+      if (u + 1 < cnt) fetch(u + 1, nr1, ngpre, ndr);
+      ok = wait_or_abort(bar(bSpFull + b), (u >> 1) & 1, abort_flag, p, 630);
+      if (ok && u >= 2) ok = wait_or_abort(bar(bAzEmpty + b), ((u >> 1) - 1) & 1, abort_flag, p, 631);
+      if (!ok) break;
+      tc_fence_after();
+      uint8_t *gA = gbase + (sAZ - base) + b * 2 * kAzBytes;
+      uint8_t *gZ = gA + kAzBytes;
+      const uint32_t tS = tmem + b * 128 + w * 32 + lane_off, tP = tS + 64;
+      float gs = 0.f, logsum = 0.f;
+      const bool diag = (u == 0);
+      const bool masked = diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0);
+      uint32_t s0[16], d0[16], s1[16], d1[16];
+      tmem_ld16(tS, s0);
+      tmem_ld16(tP, d0);
+      tmem_wait_ld_regs(s0, d0);
+      tmem_ld16(tS + 16, s1);
+      tmem_ld16(tP + 16, d1);
+      if (masked)
+        bwd_row_chunk<kFp16, true, true>(s0, d0, w * 32, quarter * 32, r, diag, p.attend_current, valid, scale2, r1f, gpre, dr,
+                                         gs, logsum, gA, gZ);
+      else
+        bwd_row_chunk<kFp16, true, false>(s0, d0, w * 32, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      tmem_wait_ld_regs(s1, d1);
+      if (masked)
+        bwd_row_chunk<kFp16, true, true>(s1, d1, w * 32 + 16, quarter * 32 + 16, r, diag, p.attend_current, valid, scale2, r1f,
+                                         gpre, dr, gs, logsum, gA, gZ);
+      else
+        bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      tc_fence_before();          // this tile's TMEM reads are done before the buffer is handed back
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bAzFull + b));
+    }
+    // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys
+    if (ok) ok = wait_or_abort(bar(bOutFull), 0, abort_flag, p, 632);
+    if (ok) {
+      tc_fence_after();
+      const TensorRef &out = w == 0 ? p.dk : p.dv;
+      const float mul = w == 0 ? p.scale : 1.f;
+      T *obase = reinterpret_cast<T *>(out.ptr) + c.boff * out.sb + (long long)h * out.sh + (c.tok0 + key0) * out.st + r;
+      const uint32_t t_acc = tmem + 256 + w * 64 + lane_off;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t va[16];
+        tmem_ld16(t_acc + ch * 16, va);
+        tmem_wait_ld();
+        if (r < p.head_dim) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const int key = key0 + ch * 16 + k;
+            if (key < c.len) obase[(long long)(ch * 16 + k) * out.st] = from_f32<T>(__uint_as_float(va[k]) * mul);
+          }
+        }
+      }
     }
   }
 
@@ -933,11 +1164,11 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   if (!p.skip_dkv && D == 128) {
-    auto kernel = tc_bwd_dkv2_kernel<kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv2::kSmem);
+    auto kernel = tc_bwd_dkv3_kernel<kFp16>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv3::kSmem);
     if (e != cudaSuccess) return e;
     dim3 grid2(2 * p.tiles_cap, p.head_cnt);
-    kernel<<<grid2, dkv2::kThreads, dkv2::kSmem, s>>>(mq, mk64, mv64, mg, p);
+    kernel<<<grid2, dkv3::kThreads, dkv3::kSmem, s>>>(mq, mk64, mv64, mg, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dkv) {
     auto kernel = tc_bwd_dkv_kernel<D, kFp16>;
