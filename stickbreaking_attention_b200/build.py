@@ -4,7 +4,9 @@ Used by ``setup.py`` and by ``__graft_entry__.build()``; can be run directly::
 
     python stickbreaking_attention_b200/build.py [--force] [--verbose]
 
-(by file path: importing the package itself already requires the built library).
+(by file path: importing the package itself already requires the built library).  Setting
+``SB_TRACE=1`` in the environment compiles the kernels' event log in (``-DSB_TRACE``); normal builds
+leave it out because even the untaken branches cost a few percent.
 """
 from __future__ import annotations
 
@@ -40,6 +42,7 @@ def _stale(target: str, deps) -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = find_nvcc()
+    extra = ("-DSB_TRACE",) if os.environ.get("SB_TRACE") == "1" else ()
     obj_dir = os.path.join(PKG_DIR, "build")
     os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(CSRC, h) for h in HEADERS]
@@ -49,7 +52,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
         objs.append(obj)
         if force or _stale(obj, [src_path, *headers]):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src_path, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", src_path, "-o", obj]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, proc in procs:
         out, _ = proc.communicate()

@@ -124,6 +124,7 @@ constexpr size_t kTraceBytes = 8 * 1024 * 16;   // workspace tail reserved for t
 
 // Event log of block (0,0): each logging thread owns a lane of 1024 entries [tag << 32 | step][SM clock]
 // and keeps its own cursor, so that logging costs two stores and no round trip.
+#ifdef SB_TRACE
 __device__ __forceinline__ void trace_event(const KParams &p, int lane_id, int &cursor, unsigned tag, unsigned step) {
   if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || cursor >= 1023) return;
   const unsigned long long t = (unsigned long long)clock64();   // SM clock: all logging threads share one SM
@@ -132,6 +133,9 @@ __device__ __forceinline__ void trace_event(const KParams &p, int lane_id, int &
   slot[1] = t;
   ++cursor;
 }
+#else   // the event log is compiled in only for diagnostic builds (nvcc -DSB_TRACE)
+__device__ __forceinline__ void trace_event(const KParams &, int, int &, unsigned, unsigned) {}
+#endif
 
 constexpr int kSimtTile = 32;
 constexpr int kTcTile = 128;

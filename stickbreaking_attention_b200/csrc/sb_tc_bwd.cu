@@ -466,27 +466,6 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp == 5) tmem_dealloc(tmem, kTmemCols);
 }
 
-// =======================================================================================================
-// dkv kernel for head sizes 72..128: one CTA per 64-key strip
-// =======================================================================================================
-// The strip's K and V stay in shared memory; the query tiles from the strip's own tile to the end of the sequence
-// stream through two Q/dO stages.  Two row-owning warpgroups take the query tiles in turn (tile i goes to warpgroup
-// i & 1, which also owns stage i & 1, its own S/dP slots in TMEM, its own A/dz tiles and its own MMA issuer), so two
-// warps are resident per scheduler and one tile's MMAs overlap the other tile's row pass.  Per tile:
-//   S = Q K^T, dP = dO V^T (128 x 64);  row pass restarted from the R1/S2 record of this strip;  then, transposed so
-//   that the MMA's M is the head dimension,  dK^T += Q^T dz  and  dV^T += dO^T A  (128 x 64, one pair per warpgroup).
-// TMEM columns: S_a 0, dP_a 64, S_b 128, dP_b 192, dK^T_a 256, dV^T_a 320, dK^T_b 384, dV^T_b 448.
-namespace dkv2 {
-constexpr int kThreads = 352;            // warps 0-7 rows, warp 8 TMA, warps 9-10 MMA issuers
-constexpr int kBN = 64;
-constexpr int kTileBytes = kBM * 128 * 2;      // Q or dO tile, 128 rows
-constexpr int kStripBytes = kBN * 128 * 2;     // K or V strip, 64 rows: two 64x64 boxes
-constexpr int kStripBox = kBN * 64 * 2;
-constexpr int kAzBytes = kBM * kBN * 2;        // A or dz tile, 128 rows x 64 keys
-constexpr int kSmem = 1024 + 2 * kStripBytes + 4 * kTileBytes + 4 * kAzBytes + 512;
-enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 9, bOutFull = 11, bNum = 12 };
-}  // namespace dkv2
-
 // One row of a 64-key strip: four 16-column chunks, TMEM read one chunk ahead.  mc0: key index of the strip's first
 // column inside its 128-key tile (for the diagonal mask).
 template <bool kFp16, bool kStoreA, bool kMasked>
@@ -517,200 +496,6 @@ __device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, 
       *mid_s2 = gpre + gs;
     }
   }
-}
-
-template <bool kFp16>
-__global__ void __launch_bounds__(dkv2::kThreads, 1)
-tc_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
-  using namespace dkv2;
-  constexpr int D = 128;
-  extern __shared__ uint8_t smem_raw[];
-  if (p.hdr[0]) return;
-  TileCoord c;
-  if (!decode_tile(p, blockIdx.x >> 1, false, c)) return;
-  const int half = blockIdx.x & 1;
-  const int J = c.idx;                         // 128-key tile of the strip
-  const int key0 = J * kBM + half * kBN;       // first key of the strip inside the sequence
-  if (key0 >= c.len) return;
-
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t *gbase = smem_raw + (base - raw);
-  const uint32_t sK = base;
-  const uint32_t sV = sK + kStripBytes;
-  const uint32_t sQ = sV + kStripBytes;              // stage w: Q at sQ + w * 2 * kTileBytes, dO right behind it
-  const uint32_t sAZ = sQ + 4 * kTileBytes;          // warpgroup w: A at sAZ + w * 2 * kAzBytes, dz right behind it
-  const uint32_t sBar = sAZ + 4 * kAzBytes;
-  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
-  volatile int *abort_flag = &ctl->abort;
-  auto bar = [&](int i) { return sBar + 8u * i; };
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int tr_cur = 0;   // cursor of this thread's event-log lane (experiments only)
-  const int hh = blockIdx.y, h = p.head0 + hh;
-  const int cnt = c.n_tiles - J;               // query tiles J .. n_tiles-1
-  const int issuers = cnt >= 2 ? 2 : 1;
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar(bKV), 1);
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(bar(bQgFull + w), 1);
-      mbar_init(bar(bQgEmpty + w), 1);
-      mbar_init(bar(bSpFull + w), 1);
-      mbar_init(bar(bAzFull + w), 4);
-      mbar_init(bar(bAzEmpty + w), 1);
-    }
-    mbar_init(bar(bOutFull), issuers);
-    ctl->abort = 0;
-    fence_barrier_init();
-  }
-  if (warp == 9) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem_base;
-
-  if (warp == 8) {
-    if (lane == 0) {
-      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
-      const int krow = (int)c.tok0 + key0;
-      mbar_arrive_expect_tx(bar(bKV), 2 * kStripBytes);
-      for (int kb = 0; kb < 2; ++kb) {
-        tma_load_4d(sK + kb * kStripBox, &tm_k, bar(bKV), kb * 64, krow, h, (int)c.boff);
-        tma_load_4d(sV + kb * kStripBox, &tm_v, bar(bKV), kb * 64, krow, h, (int)c.boff);
-      }
-      for (int i = 0; i < cnt; ++i) {
-        const int w = i & 1, u = i >> 1;
-        if (u >= 1 && !wait_or_abort(bar(bQgEmpty + w), (u - 1) & 1, abort_flag, p, 410)) break;
-        if (*abort_flag) break;
-        const int qrow = (int)c.tok0 + (J + i) * kBM;
-        const uint32_t dst = sQ + w * 2 * kTileBytes;
-        trace_event(p, 0, tr_cur, 1, i);
-        mbar_arrive_expect_tx(bar(bQgFull + w), 2 * kTileBytes);
-        for (int kb = 0; kb < 2; ++kb) {
-          tma_load_4d(dst + kb * kBoxBytes, &tm_q, bar(bQgFull + w), kb * 64, qrow, h, (int)c.boff);
-          tma_load_4d(dst + kTileBytes + kb * kBoxBytes, &tm_g, bar(bQgFull + w), kb * 64, qrow, h, (int)c.boff);
-        }
-      }
-    }
-  } else if (warp >= 9) {
-    // ------------------------------------------------ MMA issuers, one per warpgroup
-    const int w = warp - 9;
-    if (lane == 0 && w < issuers) {
-      constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);   // [128 q x 64 keys], both K-major
-      constexpr uint32_t idesc_t = idesc_f16(kBM, kBN, kFp16, true, true);     // [128 d x 64 keys], both MN-major
-      const uint32_t qaddr = sQ + w * 2 * kTileBytes, gaddr = qaddr + kTileBytes;
-      const uint32_t aaddr = sAZ + w * 2 * kAzBytes, zaddr = aaddr + kAzBytes;
-      const uint32_t tS = tmem + w * 128, tP = tS + 64, tDK = tmem + 256 + w * 128, tDV = tDK + 64;
-      const int my_cnt = (cnt - w + 1) >> 1;        // tiles w, w+2, ...
-      bool ok = wait_or_abort(bar(bKV), 0, abort_flag, p, 420);
-      for (int u = 0; ok && u < my_cnt; ++u) {
-        ok = wait_or_abort(bar(bQgFull + w), u & 1, abort_flag, p, 421);
-        if (!ok) break;
-        trace_event(p, 1 + 3 * w, tr_cur, 2 + 16 * w, 2 * u + w);
-        tc_fence_after();
-        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tS, qaddr, sK, idesc_s, false);   // S = Q K^T
-        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tP, gaddr, sV, idesc_s, false);   // dP = dO V^T
-        mma_commit(bar(bSpFull + w));
-        trace_event(p, 1 + 3 * w, tr_cur, 3 + 16 * w, 2 * u + w);
-        ok = wait_or_abort(bar(bAzFull + w), u & 1, abort_flag, p, 422);
-        if (!ok) break;
-        trace_event(p, 1 + 3 * w, tr_cur, 6 + 16 * w, 2 * u + w);
-        tc_fence_after();
-        {   // dK^T += Q^T dz,  dV^T += dO^T A: A operand rows = K (queries), M = d in two 64-blocks; B rows = K, N = 64 keys
-          const uint64_t q0 = smem_desc_sw128(qaddr, kBoxBytes, 1024), g0 = smem_desc_sw128(gaddr, kBoxBytes, 1024);
-          const uint64_t z0 = smem_desc_sw128(zaddr, 16, 1024), a0 = smem_desc_sw128(aaddr, 16, 1024);
-#pragma unroll
-          for (int ks = 0; ks < kBM / 16; ++ks) mma_f16_ss(tDK, q0 + (uint64_t)(ks * 128), z0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
-#pragma unroll
-          for (int ks = 0; ks < kBM / 16; ++ks) mma_f16_ss(tDV, g0 + (uint64_t)(ks * 128), a0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
-        }
-        mma_commit(bar(bQgEmpty + w));
-        mma_commit(bar(bAzEmpty + w));
-        trace_event(p, 1 + 3 * w, tr_cur, 7 + 16 * w, 2 * u + w);
-      }
-      if (ok) mma_commit(bar(bOutFull));
-    }
-  } else {
-    // ------------------------------------------------ rows: warpgroup w takes query tiles w, w+2, ...
-    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
-    const int w = warp >> 2;
-    const int r = threadIdx.x & 127;
-    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    const float scale2 = p.scale * kLog2e;
-    uint8_t *gA = gbase + (sAZ - base) + w * 2 * kAzBytes;
-    uint8_t *gZ = gA + kAzBytes;
-    const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
-    bool ok = true;
-    // the per-row start values of a tile come from global memory: they are fetched one tile ahead
-    auto fetch = [&](int i, float &r1f, float &gpre, float &dr) {
-      const int I = J + i;
-      const int gi = I * kBM + r;
-      const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 4 + 2 * half) * kBM + r;
-      r1f = p.bnd_r1[slot];
-      gpre = p.bnd_s2[slot];
-      dr = gi < c.len ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
-    };
-    float nr1 = 0.f, ngpre = 0.f, ndr = 0.f;
-    if (w < cnt) fetch(w, nr1, ngpre, ndr);
-    for (int i = w, u = 0; i < cnt && ok; i += 2, ++u) {
-      const int I = J + i;
-      const int gi = I * kBM + r;
-      const bool valid = gi < c.len;
-      const float r1f = nr1, gpre = ngpre, dr = ndr;
-      if (i + 2 < cnt) fetch(i + 2, nr1, ngpre, ndr);
-      ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 430);
-      if (ok && u >= 1) ok = wait_or_abort(bar(bAzEmpty + w), (u - 1) & 1, abort_flag, p, 431);
-      if (!ok) break;
-      if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, i);
-      tc_fence_after();
-      float gs = 0.f, logsum = 0.f;
-      const bool diag = (i == 0);
-      if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0))
-        strip_row_pass<kFp16, true, true>(tS, tP, r, half * kBN, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
-      else
-        strip_row_pass<kFp16, true, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
-      tc_fence_before();          // this tile's TMEM reads are done before the slots are handed back
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(bAzFull + w));
-      if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, i);
-    }
-    // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys
-    if (ok) ok = wait_or_abort(bar(bOutFull), 0, abort_flag, p, 432);
-    if (ok) {
-      tc_fence_after();
-      const TensorRef &out = w == 0 ? p.dk : p.dv;
-      const float mul = w == 0 ? p.scale : 1.f;
-      T *obase = reinterpret_cast<T *>(out.ptr) + c.boff * out.sb + (long long)h * out.sh + (c.tok0 + key0) * out.st + r;
-      const uint32_t t_a = tmem + 256 + w * 64 + lane_off;          // dK^T_a or dV^T_a
-      const uint32_t t_b = t_a + 128;                               // the other warpgroup's partial sums
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t va[16], vb[16];
-        tmem_ld16(t_a + ch * 16, va);
-        if (issuers == 2) tmem_ld16(t_b + ch * 16, vb);
-        tmem_wait_ld();
-        if (r < p.head_dim) {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const int key = key0 + ch * 16 + k;
-            float x = __uint_as_float(va[k]);
-            if (issuers == 2) x += __uint_as_float(vb[k]);
-            if (key < c.len) obase[(long long)(ch * 16 + k) * out.st] = from_f32<T>(x * mul);
-          }
-        }
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
 // =======================================================================================================
@@ -961,6 +746,7 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hh = blockIdx.y, h = p.head0 + hh;
   const int cnt = c.n_tiles - J;               // query tiles J .. n_tiles-1
+  int tr_cur = 0;   // cursor of this thread's event-log lane (diagnostics)
 
   if (threadIdx.x == 0) {
     mbar_init(bar(bKV), 1);
@@ -999,6 +785,7 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (*abort_flag) break;
         const int qrow = (int)c.tok0 + (J + u) * kBM;
         const uint32_t dst = sQ + b * 2 * kTileBytes;
+        trace_event(p, 0, tr_cur, 1, u);
         mbar_arrive_expect_tx(bar(bQgFull + b), 2 * kTileBytes);
         for (int kb = 0; kb < 2; ++kb) {
           tma_load_4d(dst + kb * kBoxBytes, &tm_q, bar(bQgFull + b), kb * 64, qrow, h, (int)c.boff);
@@ -1017,11 +804,13 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // the rows of tile u-2 have left this S/dP buffer once its A/dz tiles were signalled
         if (ok && u >= 2) ok = wait_or_abort(bar(bAzFull + b), ((u >> 1) - 1) & 1, abort_flag, p, 622);
         if (!ok) break;
+        trace_event(p, 1, tr_cur, 2, u);
         tc_fence_after();
         const uint32_t qaddr = sQ + b * 2 * kTileBytes;
         mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tmem + b * 128, qaddr, sK, idesc_s, false);
         mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tmem + b * 128 + 64, qaddr + kTileBytes, sV, idesc_s, false);
         mma_commit(bar(bSpFull + b));
+        trace_event(p, 1, tr_cur, 3, u);
       }
     }
   } else if (warp == 10) {
@@ -1033,6 +822,7 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int b = u & 1;
         ok = wait_or_abort(bar(bAzFull + b), (u >> 1) & 1, abort_flag, p, 623);
         if (!ok) break;
+        trace_event(p, 4, tr_cur, 6, u);
         tc_fence_after();
         const uint32_t qaddr = sQ + b * 2 * kTileBytes, aaddr = sAZ + b * 2 * kAzBytes;
         const uint64_t q0 = smem_desc_sw128(qaddr, kBoxBytes, 1024), g0 = smem_desc_sw128(qaddr + kTileBytes, kBoxBytes, 1024);
@@ -1045,6 +835,7 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           mma_f16_ss(tmem + 320, g0 + (uint64_t)(ks * 128), a0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
         mma_commit(bar(bQgEmpty + b));
         mma_commit(bar(bAzEmpty + b));
+        trace_event(p, 4, tr_cur, 7, u);
       }
       if (ok) mma_commit(bar(bOutFull));
     }
@@ -1077,6 +868,7 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       ok = wait_or_abort(bar(bSpFull + b), (u >> 1) & 1, abort_flag, p, 630);
       if (ok && u >= 2) ok = wait_or_abort(bar(bAzEmpty + b), ((u >> 1) - 1) & 1, abort_flag, p, 631);
       if (!ok) break;
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, u);
       tc_fence_after();
       uint8_t *gA = gbase + (sAZ - base) + b * 2 * kAzBytes;
       uint8_t *gZ = gA + kAzBytes;
@@ -1105,6 +897,7 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(bAzFull + b));
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, u);
     }
     // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys
     if (ok) ok = wait_or_abort(bar(bOutFull), 0, abort_flag, p, 632);
