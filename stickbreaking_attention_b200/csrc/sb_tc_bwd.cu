@@ -25,10 +25,10 @@ namespace sb {
 // the prefix sum of G and dz.  About 1.6 transcendentals per score (ex2, rcp / 4, lg2 / 4, ex2 / 16).
 // kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
 // The chunk is kept to 16 columns so that the unrolled code of all variants stays inside the instruction cache.
-template <bool kFp16, bool kStoreA, bool kMasked>
-__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uint32_t (&dp)[16], int c0, int mc0, int r, bool diag,
-                                              int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
-                                              float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+template <bool kMasked>
+__device__ __forceinline__ void bwd_row_chunk_values(const uint32_t (&s)[16], const uint32_t (&dp)[16], int mc0, int r, bool diag,
+                                                     int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
+                                                     float &gs, float &logsum, float (&pa)[16], float (&pz)[16]) {
   // columns (tile-local key indices) below `limit` are allowed: one compare per column, no branches
   const int limit = !row_valid ? -1 : (diag ? r + ac : 0x7fffffff);
   const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
@@ -59,13 +59,11 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
     be[4 * g + 0] = be01.x; be[4 * g + 1] = be01.y; be[4 * g + 2] = be23.x; be[4 * g + 3] = be23.y;
   }
   float W = ex2(r1 + logsum);
-  float pa[16];
 #pragma unroll
   for (int i = 15; i >= 0; --i) {
     pa[i] = be[i] * W;
     W *= ri[i];
   }
-  float pz[16];
   const float2 ndr = make_float2(-dr, -dr), gp = make_float2(gpre, gpre);
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
@@ -85,6 +83,15 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
       pz[i + 1] = row_valid ? pz[i + 1] : 0.f;
     }
   }
+}
+
+// The same, written to the 16-bit A (optional) and dz tiles; c0 addresses the output tile.
+template <bool kFp16, bool kStoreA, bool kMasked>
+__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uint32_t (&dp)[16], int c0, int mc0, int r, bool diag,
+                                              int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
+                                              float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+  float pa[16], pz[16];
+  bwd_row_chunk_values<kMasked>(s, dp, mc0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
   if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
   store_row_chunk16<kFp16>(tile_z, r, c0, pz);
 }
@@ -467,13 +474,17 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }
 
 // One row of a 64-key strip: four 16-column chunks, TMEM read one chunk ahead.  mc0: key index of the strip's first
-// column inside its 128-key tile (for the diagonal mask).
+// column inside its 128-key tile (for the diagonal mask).  empty_bar (optional) is signalled, one arrival per warp,
+// once the last S/dP columns are in registers; gate_bar (optional) is waited for before the first store to the
+// output tiles, i.e. after the first chunk's arithmetic.  Returns false if that wait gave up.
 template <bool kFp16, bool kStoreA, bool kMasked>
-__device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
+__device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
                                               float scale2, float r1, float gpre, float dr, float &gs, float &logsum,
                                               uint8_t *tile_a, uint8_t *tile_z, float *mid_r1 = nullptr,
-                                              float *mid_s2 = nullptr) {
+                                              float *mid_s2 = nullptr, uint32_t empty_bar = 0, uint32_t gate_bar = 0,
+                                              uint32_t gate_parity = 0) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
+  bool ok = true;
   tmem_ld16(ts, s0);
   tmem_ld16(tp, d0);
 #pragma unroll 1
@@ -482,12 +493,24 @@ __device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, 
     tmem_wait_ld_regs(s0, d0);
     tmem_ld16(ts + c0 + 16, s1);
     tmem_ld16(tp + c0 + 16, d1);
-    bwd_row_chunk<kFp16, kStoreA, kMasked>(s0, d0, c0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a,
-                                        tile_z);
+    {
+      float pa[16], pz[16];
+      bwd_row_chunk_values<kMasked>(s0, d0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
+      if (pair == 0 && gate_bar != 0) {
+        ok = mbar_wait(gate_bar, gate_parity);
+        tc_fence_after();
+      }
+      if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
+      store_row_chunk16<kFp16>(tile_z, r, c0, pz);
+    }
     tmem_wait_ld_regs(s1, d1);
     if (pair == 0) {
       tmem_ld16(ts + 32, s0);
       tmem_ld16(tp + 32, d0);
+    } else if (empty_bar != 0) {   // the last columns are in registers: the S/dP slots can be overwritten
+      tc_fence_before();
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
     }
     bwd_row_chunk<kFp16, kStoreA, kMasked>(s1, d1, c0 + 16, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs,
                                         logsum, tile_a, tile_z);
@@ -496,6 +519,7 @@ __device__ __forceinline__ void strip_row_pass(uint32_t ts, uint32_t tp, int r, 
       *mid_s2 = gpre + gs;
     }
   }
+  return ok;
 }
 
 // =======================================================================================================
@@ -517,7 +541,7 @@ constexpr int kKvTile = 2 * kKvBox;            // K or V sub-tile
 constexpr int kStageBytes = 2 * kKvTile;
 constexpr int kZBytes = kBM * kBN * 2;         // dz tile: 128 rows x 64 keys
 constexpr int kSmem = 1024 + 4 * kTileBytes + kStages * kStageBytes + 2 * kZBytes + 512;
-enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bDqFull = 11, bNum = 12 };
+enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bDqFull = 11, bSpEmpty = 12, bNum = 14 };
 }  // namespace dq2
 
 template <bool kFp16>
@@ -560,6 +584,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(bar(bSpFull + w), 1);
       mbar_init(bar(bZFull + w), 4);
       mbar_init(bar(bZEmpty + w), 1);
+      mbar_init(bar(bSpEmpty + w), 4);
     }
     mbar_init(bar(bDqFull), issuers);
     ctl->abort = 0;
@@ -617,17 +642,18 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (ok && w == 1 && steps_a > 0) ok = wait_or_abort(bar(bSpFull + 0), 0, abort_flag, p, 525);
       if (ok) { tc_fence_after(); issue_sp(0); }
       for (int u = 0; ok && u < my_steps; ++u) {
-        // the rows of step u are done (their S/dP reads too): next scores first, then this step's dQ
-        ok = wait_or_abort(bar(bZFull + w), u & 1, abort_flag, p, 522);
-        if (!ok) break;
+        // the rows of step u have read their S/dP (they are still computing): the next scores go first ...
         if (u + 1 < my_steps) {
-          ok = wait_or_abort(bar(bKvFull + (u + 1) % kStages), ((u + 1) / kStages) & 1, abort_flag, p, 523);
+          ok = wait_or_abort(bar(bSpEmpty + w), u & 1, abort_flag, p, 526) &&
+               wait_or_abort(bar(bKvFull + (u + 1) % kStages), ((u + 1) / kStages) & 1, abort_flag, p, 523);
           if (!ok) break;
           tc_fence_after();
           issue_sp(u + 1);
-        } else {
-          tc_fence_after();
         }
+        // ... then, once its dz tile is written, this step's dQ
+        ok = wait_or_abort(bar(bZFull + w), u & 1, abort_flag, p, 522);
+        if (!ok) break;
+        tc_fence_after();
         // dQ += dz K: dz [128 x 64] K-major, K sub-tile [64 keys x (2 x 64) columns] MN-major
         mma_kmajor_mnmajor<kBN, kKvBox>(tDQ, zaddr, sKV + (u % kStages) * kStageBytes, idesc_dq, u > 0);
         mma_commit(bar(bZEmpty + w));
@@ -662,21 +688,29 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     bool ok = true;
     for (int u = 0; u < my_steps && ok; ++u) {
       ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 530);
-      if (ok && u >= 1) ok = wait_or_abort(bar(bZEmpty + w), (u - 1) & 1, abort_flag, p, 531);
       if (!ok) break;
       tc_fence_after();
+      // the dz tile is still being read by the previous step's dQ MMAs: waited for inside the pass, before its first store
+      const uint32_t gate = u >= 1 ? bar(bZEmpty + w) : 0u, gate_parity = (u - 1) & 1;
       const float r1f = (float)r1;
       float *rec_r1 = p.bnd_r1 + rec0 + (long long)u * (2 * kBM);   // quarter 2 (u & 1) of key tile u >> 1
       float *rec_s2 = p.bnd_s2 + rec0 + (long long)u * (2 * kBM);
       rec_r1[0] = r1f;
       rec_s2[0] = gpre;
       float gs = 0.f, logsum = 0.f;
+      bool pass_ok;
       if (u >= 2 * I)
-        strip_row_pass<kFp16, false, true>(tS, tP, r, (u - 2 * I) * kBN, true, p.attend_current, true, scale2, r1f, gpre, dr,
-                                           gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM);
+        pass_ok = strip_row_pass<kFp16, false, true>(tS, tP, r, (u - 2 * I) * kBN, true, p.attend_current, true, scale2, r1f, gpre,
+                                                     dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w),
+                                                     gate, gate_parity);
       else
-        strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
-                                            rec_r1 + kBM, rec_s2 + kBM);
+        pass_ok = strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
+                                                      rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w), gate, gate_parity);
+      if (!pass_ok) {   // the bounded wait inside the pass gave up
+        *abort_flag = 1;
+        if (p.status != nullptr) { p.status[0] = SB_DEV_WAIT_TIMEOUT; p.status[1] = 531; }
+        ok = false;
+      }
       r1 += (double)logsum;
       gpre += gs;
       tc_fence_before();          // this step's TMEM reads are done before the slots are handed back
