@@ -732,47 +732,48 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }
 
 // =======================================================================================================
-// dkv kernel for head sizes 72..128, pipelined: one CTA per 64-key strip, all eight row warps on one query tile
+// dkv kernel for head sizes 72..128, pipelined: one CTA per 128-key tile, all eight row warps on one query tile
 // =======================================================================================================
-// Warps 0-3 own key columns 0..31 of the strip and warps 4-7 columns 32..63 for the same 128 query rows; each half
-// restarts from its own R1/S2 record (the dq kernel records them every 32 keys), so the halves are independent.
-// With S/dP and the A/dz tiles double-buffered and the Q/dO tiles in a two-stage ring, the S/dP MMAs of tile u+1
-// (issuer warp 9) and the dK^T/dV^T MMAs of tile u-1 (issuer warp 10) run while the rows of tile u are processed.
-// TMEM columns: S[b] at 128 b, dP[b] at 128 b + 64, dK^T 256, dV^T 320.
-namespace dkv3 {
+// The key tile is handled as two 64-key strips (h = 0, 1) that share every Q/dO tile: a step is one query tile
+// against one strip, and the two steps of a query tile use the same Q/dO stage, so Q/dO are loaded once per
+// 128 keys.  Within a step, warps 0-3 own key columns 0..31 of the strip and warps 4-7 columns 32..63 for the same
+// 128 query rows; each group restarts from its own R1/S2 record (the dq kernel records them every 32 keys), so the
+// groups are independent.  S/dP are double-buffered in TMEM and the Q/dO tiles sit in a two-stage ring: the S/dP
+// MMAs of step g+1 (issuer warp 9) and the dK^T/dV^T MMAs of step g-1 (issuer warp 10) run while the rows of
+// step g are processed.  The A/dz tiles are single-buffered; the rows wait for the previous step's dK^T/dV^T MMAs
+// only before their first store, i.e. after a quarter of the step's arithmetic.
+// TMEM columns: S[slot] at 128 slot, dP[slot] at 128 slot + 64, dK^T[h] at 256 + 128 h, dV^T[h] at 320 + 128 h.
+namespace dkv4 {
 constexpr int kThreads = 352;
 constexpr int kBN = 64;
-constexpr int kTileBytes = kBM * 128 * 2;      // Q or dO tile
-constexpr int kStripBytes = kBN * 128 * 2;     // K or V strip: two 64x64 boxes
-constexpr int kStripBox = kBN * 64 * 2;
+constexpr int kTileBytes = kBM * 128 * 2;      // Q, dO, K or V tile: two 128 x 64 boxes
+constexpr int kStripOffset = kBN * 128;        // byte offset of strip 1 inside a box (64 rows of 128 bytes)
 constexpr int kAzBytes = kBM * kBN * 2;        // A or dz tile, 128 rows x 64 keys
-constexpr int kSmem = 1024 + 2 * kStripBytes + 4 * kTileBytes + 4 * kAzBytes + 512;
-enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bAzFull = 7, bAzEmpty = 9, bOutFull = 11, bNum = 12 };
-}  // namespace dkv3
+constexpr int kSmem = 1024 + 2 * kTileBytes + 4 * kTileBytes + 2 * kAzBytes + 512;
+enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bSpEmpty = 7, bAzFull = 9, bAzEmpty = 10, bOutFull = 11, bNum = 12 };
+}  // namespace dkv4
 
 template <bool kFp16>
-__global__ void __launch_bounds__(dkv3::kThreads, 1)
-tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+__global__ void __launch_bounds__(dkv4::kThreads, 1)
+tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
-  using namespace dkv3;
+  using namespace dkv4;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x >> 1, false, c)) return;
-  const int half = blockIdx.x & 1;
-  const int J = c.idx;                         // 128-key tile of the strip
-  const int key0 = J * kBM + half * kBN;       // first key of the strip inside the sequence
-  if (key0 >= c.len) return;
+  if (!decode_tile(p, blockIdx.x, false, c)) return;
+  const int J = c.idx;                         // the 128-key tile
+  const int n_halves = J * kBM + kBN < c.len ? 2 : 1;   // the sequence may end inside the first strip
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *gbase = smem_raw + (base - raw);
   const uint32_t sK = base;
-  const uint32_t sV = sK + kStripBytes;
-  const uint32_t sQ = sV + kStripBytes;              // stage b: Q at sQ + b * 2 * kTileBytes, dO right behind it
-  const uint32_t sAZ = sQ + 4 * kTileBytes;          // buffer b: A at sAZ + b * 2 * kAzBytes, dz right behind it
-  const uint32_t sBar = sAZ + 4 * kAzBytes;
+  const uint32_t sV = sK + kTileBytes;
+  const uint32_t sQ = sV + kTileBytes;               // stage b: Q at sQ + b * 2 * kTileBytes, dO right behind it
+  const uint32_t sAZ = sQ + 4 * kTileBytes;          // A, then dz
+  const uint32_t sBar = sAZ + 2 * kAzBytes;
   Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
   volatile int *abort_flag = &ctl->abort;
   auto bar = [&](int i) { return sBar + 8u * i; };
@@ -780,6 +781,8 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hh = blockIdx.y, h = p.head0 + hh;
   const int cnt = c.n_tiles - J;               // query tiles J .. n_tiles-1
+  const int n_steps = cnt * n_halves;          // step g: query tile J + g / n_halves, strip g % n_halves
+  const int hshift = n_halves - 1;
   int tr_cur = 0;   // cursor of this thread's event-log lane (diagnostics)
 
   if (threadIdx.x == 0) {
@@ -788,9 +791,10 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(bar(bQgFull + b), 1);
       mbar_init(bar(bQgEmpty + b), 1);
       mbar_init(bar(bSpFull + b), 1);
-      mbar_init(bar(bAzFull + b), 8);
-      mbar_init(bar(bAzEmpty + b), 1);
+      mbar_init(bar(bSpEmpty + b), 8);
     }
+    mbar_init(bar(bAzFull), 8);
+    mbar_init(bar(bAzEmpty), 1);
     mbar_init(bar(bOutFull), 1);
     ctl->abort = 0;
     fence_barrier_init();
@@ -807,11 +811,11 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 8) {
     if (lane == 0) {
       prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
-      const int krow = (int)c.tok0 + key0;
-      mbar_arrive_expect_tx(bar(bKV), 2 * kStripBytes);
+      const int krow = (int)c.tok0 + J * kBM;
+      mbar_arrive_expect_tx(bar(bKV), 2 * kTileBytes);
       for (int kb = 0; kb < 2; ++kb) {
-        tma_load_4d(sK + kb * kStripBox, &tm_k, bar(bKV), kb * 64, krow, h, (int)c.boff);
-        tma_load_4d(sV + kb * kStripBox, &tm_v, bar(bKV), kb * 64, krow, h, (int)c.boff);
+        tma_load_4d(sK + kb * kBoxBytes, &tm_k, bar(bKV), kb * 64, krow, h, (int)c.boff);
+        tma_load_4d(sV + kb * kBoxBytes, &tm_v, bar(bKV), kb * 64, krow, h, (int)c.boff);
       }
       for (int u = 0; u < cnt; ++u) {
         const int b = u & 1;
@@ -832,44 +836,45 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);
       bool ok = wait_or_abort(bar(bKV), 0, abort_flag, p, 620);
-      for (int u = 0; ok && u < cnt; ++u) {
-        const int b = u & 1;
+      for (int g = 0; ok && g < n_steps; ++g) {
+        const int u = g >> hshift, hf = g & hshift, b = u & 1, slot = g & 1;
         ok = wait_or_abort(bar(bQgFull + b), (u >> 1) & 1, abort_flag, p, 621);
-        // the rows of tile u-2 have left this S/dP buffer once its A/dz tiles were signalled
-        if (ok && u >= 2) ok = wait_or_abort(bar(bAzFull + b), ((u >> 1) - 1) & 1, abort_flag, p, 622);
+        // the rows of step g-2 have read this S/dP slot
+        if (ok && g >= 2) ok = wait_or_abort(bar(bSpEmpty + slot), ((g >> 1) - 1) & 1, abort_flag, p, 622);
         if (!ok) break;
-        trace_event(p, 1, tr_cur, 2, u);
+        trace_event(p, 1, tr_cur, 2, g);
         tc_fence_after();
         const uint32_t qaddr = sQ + b * 2 * kTileBytes;
-        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tmem + b * 128, qaddr, sK, idesc_s, false);
-        mma_kmajor_kmajor<D, kBoxBytes, kStripBox>(tmem + b * 128 + 64, qaddr + kTileBytes, sV, idesc_s, false);
-        mma_commit(bar(bSpFull + b));
-        trace_event(p, 1, tr_cur, 3, u);
+        mma_kmajor_kmajor<D>(tmem + slot * 128, qaddr, sK + hf * kStripOffset, idesc_s, false);
+        mma_kmajor_kmajor<D>(tmem + slot * 128 + 64, qaddr + kTileBytes, sV + hf * kStripOffset, idesc_s, false);
+        mma_commit(bar(bSpFull + slot));
+        trace_event(p, 1, tr_cur, 3, g);
       }
     }
   } else if (warp == 10) {
     // ------------------------------------------------ issuer of dK^T += Q^T dz and dV^T += dO^T A (128 x 64)
     if (lane == 0) {
       constexpr uint32_t idesc_t = idesc_f16(kBM, kBN, kFp16, true, true);
+      const uint64_t a0 = smem_desc_sw128(sAZ, 16, 1024), z0 = smem_desc_sw128(sAZ + kAzBytes, 16, 1024);
       bool ok = true;
-      for (int u = 0; ok && u < cnt; ++u) {
-        const int b = u & 1;
-        ok = wait_or_abort(bar(bAzFull + b), (u >> 1) & 1, abort_flag, p, 623);
+      for (int g = 0; ok && g < n_steps; ++g) {
+        const int u = g >> hshift, hf = g & hshift, b = u & 1;
+        ok = wait_or_abort(bar(bAzFull), g & 1, abort_flag, p, 623);
         if (!ok) break;
-        trace_event(p, 4, tr_cur, 6, u);
+        trace_event(p, 4, tr_cur, 6, g);
         tc_fence_after();
-        const uint32_t qaddr = sQ + b * 2 * kTileBytes, aaddr = sAZ + b * 2 * kAzBytes;
+        const uint32_t qaddr = sQ + b * 2 * kTileBytes;
         const uint64_t q0 = smem_desc_sw128(qaddr, kBoxBytes, 1024), g0 = smem_desc_sw128(qaddr + kTileBytes, kBoxBytes, 1024);
-        const uint64_t a0 = smem_desc_sw128(aaddr, 16, 1024), z0 = smem_desc_sw128(aaddr + kAzBytes, 16, 1024);
+        const uint32_t t_dk = tmem + 256 + hf * 128, t_dv = t_dk + 64;
 #pragma unroll
         for (int ks = 0; ks < kBM / 16; ++ks)
-          mma_f16_ss(tmem + 256, q0 + (uint64_t)(ks * 128), z0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
+          mma_f16_ss(t_dk, q0 + (uint64_t)(ks * 128), z0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
 #pragma unroll
         for (int ks = 0; ks < kBM / 16; ++ks)
-          mma_f16_ss(tmem + 320, g0 + (uint64_t)(ks * 128), a0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
-        mma_commit(bar(bQgEmpty + b));
-        mma_commit(bar(bAzEmpty + b));
-        trace_event(p, 4, tr_cur, 7, u);
+          mma_f16_ss(t_dv, g0 + (uint64_t)(ks * 128), a0 + (uint64_t)(ks * 128), idesc_t, u > 0 || ks > 0);
+        mma_commit(bar(bAzEmpty));
+        if (hf == hshift) mma_commit(bar(bQgEmpty + b));   // the tile's last strip: its Q/dO stage is free
+        trace_event(p, 4, tr_cur, 7, g);
       }
       if (ok) mma_commit(bar(bOutFull));
     }
@@ -880,33 +885,32 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int r = threadIdx.x & 127;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float scale2 = p.scale * kLog2e;
-    const int quarter = 2 * half + w;            // which 32-key quarter of the 128-key tile
     bool ok = true;
-    // the per-row start values of a tile come from global memory: they are fetched one tile ahead
-    auto fetch = [&](int u, float &r1f, float &gpre, float &dr) {
-      const int I = J + u;
+    // the per-row start values of a step come from global memory: they are fetched one step ahead
+    auto fetch = [&](int g, float &r1f, float &gpre, float &dr) {
+      const int I = J + (g >> hshift), quarter = 2 * (g & hshift) + w;   // which 32-key quarter of the 128-key tile
       const int gi = I * kBM + r;
       const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 4 + quarter) * kBM + r;
       r1f = p.bnd_r1[slot];
       gpre = p.bnd_s2[slot];
       dr = gi < c.len ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
     };
+    uint8_t *gA = gbase + (sAZ - base);
+    uint8_t *gZ = gA + kAzBytes;
     float nr1, ngpre, ndr;
     fetch(0, nr1, ngpre, ndr);
-    for (int u = 0; u < cnt && ok; ++u) {
-      const int b = u & 1;
+    for (int g = 0; g < n_steps && ok; ++g) {
+      const int u = g >> hshift, hf = g & hshift, slot = g & 1;
       const int I = J + u;
+      const int quarter = 2 * hf + w;
       const bool valid = I * kBM + r < c.len;
       const float r1f = nr1, gpre = ngpre, dr = ndr;
-      if (u + 1 < cnt) fetch(u + 1, nr1, ngpre, ndr);
-      ok = wait_or_abort(bar(bSpFull + b), (u >> 1) & 1, abort_flag, p, 630);
-      if (ok && u >= 2) ok = wait_or_abort(bar(bAzEmpty + b), ((u >> 1) - 1) & 1, abort_flag, p, 631);
+      if (g + 1 < n_steps) fetch(g + 1, nr1, ngpre, ndr);
+      ok = wait_or_abort(bar(bSpFull + slot), (g >> 1) & 1, abort_flag, p, 630);
       if (!ok) break;
-      if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, u);
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, g);
       tc_fence_after();
-      uint8_t *gA = gbase + (sAZ - base) + b * 2 * kAzBytes;
-      uint8_t *gZ = gA + kAzBytes;
-      const uint32_t tS = tmem + b * 128 + w * 32 + lane_off, tP = tS + 64;
+      const uint32_t tS = tmem + slot * 128 + w * 32 + lane_off, tP = tS + 64;
       float gs = 0.f, logsum = 0.f;
       const bool diag = (u == 0);
       const bool masked = diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0);
@@ -916,22 +920,33 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_wait_ld_regs(s0, d0);
       tmem_ld16(tS + 16, s1);
       tmem_ld16(tP + 16, d1);
-      if (masked)
-        bwd_row_chunk<kFp16, true, true>(s0, d0, w * 32, quarter * 32, r, diag, p.attend_current, valid, scale2, r1f, gpre, dr,
-                                         gs, logsum, gA, gZ);
-      else
-        bwd_row_chunk<kFp16, true, false>(s0, d0, w * 32, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      {
+        float pa[16], pz[16];
+        if (masked)
+          bwd_row_chunk_values<true>(s0, d0, quarter * 32, r, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
+        else
+          bwd_row_chunk_values<false>(s0, d0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
+        // the A/dz tiles are still being read by the previous step's MMAs
+        if (g >= 1) {
+          ok = wait_or_abort(bar(bAzEmpty), (g - 1) & 1, abort_flag, p, 631);
+          tc_fence_after();
+        }
+        store_row_chunk16<kFp16>(gA, r, w * 32, pa);
+        store_row_chunk16<kFp16>(gZ, r, w * 32, pz);
+      }
       tmem_wait_ld_regs(s1, d1);
+      tc_fence_before();          // this step's TMEM reads are done: the S/dP slot is handed back
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bSpEmpty + slot));
       if (masked)
         bwd_row_chunk<kFp16, true, true>(s1, d1, w * 32 + 16, quarter * 32 + 16, r, diag, p.attend_current, valid, scale2, r1f,
                                          gpre, dr, gs, logsum, gA, gZ);
       else
         bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
-      tc_fence_before();          // this tile's TMEM reads are done before the buffer is handed back
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(bAzFull + b));
-      if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, u);
+      if (lane == 0) mbar_arrive(bar(bAzFull));
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, g);
     }
     // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys
     if (ok) ok = wait_or_abort(bar(bOutFull), 0, abort_flag, p, 632);
@@ -939,17 +954,18 @@ tc_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after();
       const TensorRef &out = w == 0 ? p.dk : p.dv;
       const float mul = w == 0 ? p.scale : 1.f;
-      T *obase = reinterpret_cast<T *>(out.ptr) + c.boff * out.sb + (long long)h * out.sh + (c.tok0 + key0) * out.st + r;
-      const uint32_t t_acc = tmem + 256 + w * 64 + lane_off;
+      T *obase = reinterpret_cast<T *>(out.ptr) + c.boff * out.sb + (long long)h * out.sh + (c.tok0 + J * kBM) * out.st + r;
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 4 * n_halves; ++ch) {
+        // 16 keys per load: strip ch / 4, columns (ch % 4) * 16 of this warpgroup's accumulator
+        const uint32_t t_acc = tmem + 256 + (ch >> 2) * 128 + w * 64 + (ch & 3) * 16 + lane_off;
         uint32_t va[16];
-        tmem_ld16(t_acc + ch * 16, va);
+        tmem_ld16(t_acc, va);
         tmem_wait_ld();
         if (r < p.head_dim) {
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
-            const int key = key0 + ch * 16 + k;
+            const int key = J * kBM + ch * 16 + k;
             if (key < c.len) obase[(long long)(ch * 16 + k) * out.st] = from_f32<T>(__uint_as_float(va[k]) * mul);
           }
         }
@@ -991,11 +1007,10 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   if (!p.skip_dkv && D == 128) {
-    auto kernel = tc_bwd_dkv3_kernel<kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv3::kSmem);
+    auto kernel = tc_bwd_dkv4_kernel<kFp16>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv4::kSmem);
     if (e != cudaSuccess) return e;
-    dim3 grid2(2 * p.tiles_cap, p.head_cnt);
-    kernel<<<grid2, dkv3::kThreads, dkv3::kSmem, s>>>(mq, mk64, mv64, mg, p);
+    kernel<<<grid, dkv4::kThreads, dkv4::kSmem, s>>>(mq, mk, mv, mg, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dkv) {
     auto kernel = tc_bwd_dkv_kernel<D, kFp16>;
