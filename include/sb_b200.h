@@ -137,8 +137,9 @@ SB_EXPORT int sb_bwd(const SbParams *p, void *stream);
  * that array until the process exits.
  *
  * Same results as sb_fwd.  Calls that need more scratch than the array holds (sb_workspace_bytes(p, 0) >
- * SB_STATIC_SCRATCH_BYTES, i.e. beyond about 5400 packed sequences; a fixed-length batch always fits) return
- * SB_ERR_WORKSPACE with a message and launch nothing.  The function calls no cudaMalloc, cudaFree or any
+ * SB_STATIC_SCRATCH_BYTES; a packed batch needs about 20 bytes per sequence plus 8 bytes per 128 tokens, so
+ * e.g. 2500 sequences in 65536 tokens fit; a fixed-length batch always fits) return SB_ERR_WORKSPACE with a
+ * message and launch nothing.  The function calls no cudaMalloc, cudaFree or any
  * other allocating routine.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device

@@ -31,7 +31,7 @@ struct Plan {
   int n_max;
   int max_seqlen;
   long long pairs_cap;
-  size_t off_tile_prefix, off_pair_prefix, off_bnd;
+  size_t off_tile_prefix, off_pair_prefix, off_order, off_order2, off_bnd;
   int bnd_halves;             // boundary records per (query tile, key tile) pair
   size_t bnd_bytes_per_head;  // one of the two arrays
   int chunk_heads;
@@ -92,7 +92,10 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   if (pl.tiles_cap < 1) pl.tiles_cap = 1;
   pl.off_tile_prefix = 256;
   pl.off_pair_prefix = align_up(pl.off_tile_prefix + sizeof(int) * (size_t)(p->num_seq + 1), 256);
-  pl.off_bnd = align_up(pl.off_pair_prefix + sizeof(long long) * (size_t)(p->num_seq + 1), 256);
+  pl.off_order = align_up(pl.off_pair_prefix + sizeof(long long) * (size_t)(p->num_seq + 1), 256);
+  const size_t order_bytes = p->cu_seqlens != nullptr ? align_up(sizeof(int2) * (size_t)pl.tiles_cap, 256) : 0;
+  pl.off_order2 = pl.off_order + order_bytes;                       // every second tile: the backward's dq kernel
+  pl.off_bnd = pl.off_order2 + ((backward && tc) ? order_bytes : 0);
   // the tensor-core path records the carried values four times per 128-key tile
   pl.bnd_halves = tc ? 4 : 1;   // keys 0, 32, 64, 96 of every 128-key tile
   pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * pl.bnd_halves * sizeof(float), 256);
@@ -162,6 +165,7 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   k.scale = p->logit_scale;
   k.check_leading_zero = (p->cu_seqlens != nullptr && (p->flags & SB_FLAG_CHECK_LEADING_ZERO)) ? 1 : 0;
   k.dbg = p->reserved & 0xff;
+  k.trace_mode = (p->reserved >> 8) & 3;
   k.trace = (p->reserved & 0x100) ? reinterpret_cast<unsigned long long *>(ws_end - kTraceBytes) : nullptr;
   k.skip_dq = (p->flags & SB_FLAG_BWD_SKIP_DQ) ? 1 : 0;
   k.skip_dkv = (p->flags & SB_FLAG_BWD_SKIP_DKV) ? 1 : 0;
@@ -170,6 +174,10 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   k.hdr = reinterpret_cast<int *>(ws);
   k.tile_prefix = reinterpret_cast<int *>(ws + pl.off_tile_prefix);
   k.pair_prefix = reinterpret_cast<long long *>(ws + pl.off_pair_prefix);
+  if (p->cu_seqlens != nullptr) {
+    k.order = reinterpret_cast<const int2 *>(ws + pl.off_order);
+    if (pl.off_bnd != pl.off_order2) k.order2 = reinterpret_cast<const int2 *>(ws + pl.off_order2);
+  }
   k.bnd_r1 = reinterpret_cast<float *>(ws + pl.off_bnd);
   k.bnd_s2 = reinterpret_cast<float *>(ws + pl.off_bnd + pl.bnd_bytes_per_head * pl.chunk_heads);
   k.pairs_cap = (long long)(pl.bnd_bytes_per_head / ((size_t)pl.tile * pl.bnd_halves * sizeof(float)));
@@ -242,7 +250,7 @@ static int run_fwd_static_scratch(const SbParams *p, void *stream) {
   if (pl.total_fwd > (size_t)SB_STATIC_SCRATCH_BYTES)
     return fail(SB_ERR_WORKSPACE,
                 "sb_fwd_static_scratch: this call needs %zu bytes of scratch but the built-in scratch holds %d "
-                "(about 5400 packed sequences); use sb_fwd with a caller-provided workspace",
+                "(about 20 bytes per packed sequence plus 8 per 128 tokens); use sb_fwd with a caller-provided workspace",
                 pl.total_fwd, (int)SB_STATIC_SCRATCH_BYTES);
   if ((rc = device_ok())) return rc;
   void *scratch = nullptr;

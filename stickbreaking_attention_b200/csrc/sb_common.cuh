@@ -38,10 +38,13 @@ struct KParams {
   int max_seqlen;
   int check_leading_zero;  // the element before cu[0] must be 0
   int skip_dq, skip_dkv;   // timing aids: leave one of the two backward kernels out
+  const int2 *order;       // packed batches: work items by descending weight, see decode_item
+  const int2 *order2;      // the same for every second tile (backward only)
+  int trace_mode;          // diagnostics builds: bit 1 = log every block's SM, start, first row work and end time
   int dbg;                 // experiments only (SbParams.reserved): 0 = normal arithmetic
   unsigned long long *trace;  // experiments only: event log of block (0,0) in the workspace tail, or nullptr
   // workspace views
-  int *hdr;            // [0] abort flag, [1] end of the last sequence (varlen)
+  int *hdr;            // [0] abort flag, [1] end of the last sequence (varlen), [2] / [3] entries of order / order2
   int *tile_prefix;    // [num_seq + 1]  exclusive prefix of tiles per sequence (varlen)
   long long *pair_prefix;  // [num_seq + 1] exclusive prefix of n(n+1)/2 (varlen)
   float *bnd_r1;       // [head_cnt][pairs_cap][tile]  suffix sums of log(1-beta) at tile starts
@@ -66,37 +69,60 @@ __device__ __forceinline__ long long load_cu(const KParams &p, int i) {
                 : (long long)reinterpret_cast<const int *>(p.cu)[i];
 }
 
-// Maps a flat work-item number to its sequence and tile.  Heavier (later) query tiles come first
-// inside a sequence when `reverse` is set, so that the longest-running blocks start earliest.
-__device__ __forceinline__ bool decode_tile(const KParams &p, int item, bool reverse, TileCoord &c) {
+// Maps a work-item number to its sequence and tile.  Items are ordered by weight across ALL sequences: the tile with
+// the most key (or query) tiles to visit comes first, so that the blocks that run longest start earliest and the
+// last blocks of a launch are the short ones.  For a packed batch the order is a table the prep kernel writes
+// (entries (sequence, k), k = tile index counted so that larger means heavier; `group` > 1 lists every group-th
+// tile only); for a fixed-length batch it is arithmetic.  `reverse`: the heavy tiles are the late ones (a query
+// tile sees all earlier keys); otherwise the early ones (a key tile is seen by all later queries).
+__device__ __forceinline__ bool decode_item(const KParams &p, int item, int group, bool reverse, TileCoord &c) {
+  int s, k;
   if (p.cu == nullptr) {
     const int n = (int)((p.tokens + p.tile - 1) / p.tile);
-    if (item >= n * p.batch) return false;
-    c.seq = item / n;
-    c.idx = item - c.seq * n;
+    const int m = (n + group - 1) / group;
+    if (item >= m * p.batch) return false;
+    const int j = item / p.batch;
+    s = item - j * p.batch;
+    k = (m - 1 - j) * group;
     c.n_tiles = n;
     c.len = (int)p.tokens;
     c.tok0 = 0;
-    c.boff = c.seq;
-    c.pair0 = (long long)c.seq * ((long long)n * (n + 1) / 2);
+    c.boff = s;
+    c.pair0 = (long long)s * ((long long)n * (n + 1) / 2);
   } else {
-    const int total = p.tile_prefix[p.num_seq];
-    if (item >= total) return false;
-    int lo = 0, hi = p.num_seq - 1;  // last sequence whose prefix <= item
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (p.tile_prefix[mid] <= item) lo = mid; else hi = mid - 1;
-    }
-    c.seq = lo;
-    c.idx = item - p.tile_prefix[lo];
-    c.n_tiles = p.tile_prefix[lo + 1] - p.tile_prefix[lo];
-    c.tok0 = lo == 0 ? 0 : load_cu(p, lo - 1);
-    c.len = (int)(load_cu(p, lo) - c.tok0);
+    if (item >= p.hdr[group == 1 ? 2 : 3]) return false;
+    const int2 e = (group == 1 ? p.order : p.order2)[item];
+    s = e.x;
+    k = e.y;
+    c.n_tiles = p.tile_prefix[s + 1] - p.tile_prefix[s];
+    c.tok0 = s == 0 ? 0 : load_cu(p, s - 1);
+    c.len = (int)(load_cu(p, s) - c.tok0);
     c.boff = 0;
-    c.pair0 = p.pair_prefix[lo];
+    c.pair0 = p.pair_prefix[s];
   }
-  if (reverse) c.idx = c.n_tiles - 1 - c.idx;
+  c.seq = s;
+  c.idx = reverse ? k : c.n_tiles - 1 - k;
   return true;
+}
+__device__ __forceinline__ bool decode_tile(const KParams &p, int item, bool reverse, TileCoord &c) {
+  return decode_item(p, item, 1, reverse, c);
+}
+// One-dimensional grids: block = item * head_cnt + head, so that equal-weight items of all heads are neighbours.
+__device__ __forceinline__ bool decode_block(const KParams &p, int group, bool reverse, TileCoord &c, int &hh) {
+  const int item = blockIdx.x / p.head_cnt;
+  hh = blockIdx.x - item * p.head_cnt;
+  return decode_item(p, item, group, reverse, c);
+}
+// Blocks to launch for such a grid (an upper bound for packed batches: surplus blocks leave at once).
+inline long long item_blocks(const KParams &p, int group) {
+  long long items;
+  if (p.cu == nullptr) {
+    const long long n = (p.tokens + p.tile - 1) / p.tile;
+    items = ((n + group - 1) / group) * p.batch;
+  } else {
+    items = group == 1 ? p.tiles_cap : (p.tiles_cap + p.num_seq + 1) / 2;
+  }
+  return items * p.head_cnt;
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T x);
@@ -126,14 +152,26 @@ constexpr size_t kTraceBytes = 8 * 1024 * 16;   // workspace tail reserved for t
 // and keeps its own cursor, so that logging costs two stores and no round trip.
 #ifdef SB_TRACE
 __device__ __forceinline__ void trace_event(const KParams &p, int lane_id, int &cursor, unsigned tag, unsigned step) {
-  if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || cursor >= 1023) return;
+  if (p.trace == nullptr || (p.trace_mode & 2) || blockIdx.x != 0 || blockIdx.y != 0 || cursor >= 1023) return;
   const unsigned long long t = (unsigned long long)clock64();   // SM clock: all logging threads share one SM
   unsigned long long *slot = p.trace + ((size_t)lane_id * 1024 + cursor) * 2;
   slot[0] = ((unsigned long long)tag << 32) | step;
   slot[1] = t;
   ++cursor;
 }
+// Block schedule log: [linear block id][3] = (globaltimer ns << 10 | SM id) at entry, first row work and exit.
+__device__ __forceinline__ void trace_block(const KParams &p, int which) {
+  if (p.trace == nullptr || !(p.trace_mode & 2)) return;
+  const unsigned lin = blockIdx.y * gridDim.x + blockIdx.x;
+  if (lin >= 5400) return;
+  unsigned long long t;
+  unsigned smid;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  p.trace[lin * 3 + which] = (t << 10) | smid;
+}
 #else   // the event log is compiled in only for diagnostic builds (nvcc -DSB_TRACE)
+__device__ __forceinline__ void trace_block(const KParams &, int) {}
 __device__ __forceinline__ void trace_event(const KParams &, int, int &, unsigned, unsigned) {}
 #endif
 

@@ -20,7 +20,54 @@ namespace sb {
 // ------------------------------------------------------------------------------------------------
 // Sequence table: exclusive prefix of tiles per sequence and of (query tile, key tile) pairs.
 // ------------------------------------------------------------------------------------------------
+// Work items by descending weight (see decode_item): a counting sort over the classes k / group, the heaviest
+// class first; inside a class the order is whatever the shared-memory atomics give, which does not matter.
+constexpr int kMaxClasses = 8192;
+__device__ __forceinline__ int seq_tiles(const KParams &p, int s) {
+  const long long start = s == 0 ? 0 : load_cu(p, s - 1);
+  const long long len = load_cu(p, s) - start;
+  if (len < 0 || len > p.max_seqlen) return 0;
+  return (int)((len + p.tile - 1) / p.tile);
+}
+__device__ void build_order(const KParams &p, int group, int2 *out, int hdr_slot, int *s_cls) {
+  const int t = threadIdx.x;
+  const int m_max = (p.n_max + group - 1) / group;
+  if (m_max > kMaxClasses) {   // sequences beyond a million tokens: sequence by sequence, serially
+    if (t == 0) {
+      int pos = 0;
+      for (int s = 0; s < p.num_seq; ++s)
+        for (int j = (seq_tiles(p, s) + group - 1) / group - 1; j >= 0; --j) out[pos++] = make_int2(s, j * group);
+      p.hdr[hdr_slot] = pos;
+    }
+    __syncthreads();
+    return;
+  }
+  for (int j = t; j < m_max; j += blockDim.x) s_cls[j] = 0;
+  __syncthreads();
+  for (int s = t; s < p.num_seq; s += blockDim.x) {
+    const int m = (seq_tiles(p, s) + group - 1) / group;
+    if (m > 0) atomicAdd(&s_cls[m - 1], 1);
+  }
+  __syncthreads();
+  if (t == 0) {   // s_cls[j]: sequences whose last class is j  ->  first position of class j
+    int longer = 0, pos = 0;
+    for (int j = m_max - 1; j >= 0; --j) {
+      longer += s_cls[j];
+      s_cls[j] = pos;
+      pos += longer;
+    }
+    p.hdr[hdr_slot] = pos;
+  }
+  __syncthreads();
+  for (int s = t; s < p.num_seq; s += blockDim.x) {
+    const int m = (seq_tiles(p, s) + group - 1) / group;
+    for (int j = 0; j < m; ++j) out[atomicAdd(&s_cls[j], 1)] = make_int2(s, j * group);
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(256) prep_kernel(KParams p) {
+  __shared__ int s_cls[kMaxClasses];
   __shared__ long long s_tiles[256];
   __shared__ long long s_pairs[256];
   const int t = threadIdx.x;
@@ -73,10 +120,14 @@ __global__ void __launch_bounds__(256) prep_kernel(KParams p) {
     tiles += n;
     pairs += n * (n + 1) / 2;
   }
+  __syncthreads();
+  if (p.hdr[0]) return;   // bad cu_seqlens: no kernel will look at the order
+  build_order(p, 1, const_cast<int2 *>(p.order), 2, s_cls);
+  if (p.order2 != nullptr) build_order(p, 2, const_cast<int2 *>(p.order2), 3, s_cls);
 }
 
 __global__ void clear_hdr_kernel(int *hdr, unsigned long long *trace) {
-  if (threadIdx.x < 4) hdr[threadIdx.x] = 0;
+  if (threadIdx.x < 8) hdr[threadIdx.x] = 0;
   if (trace != nullptr)
     for (int i = threadIdx.x; i < (int)(kTraceBytes / 8); i += blockDim.x) trace[i] = 0;
 }

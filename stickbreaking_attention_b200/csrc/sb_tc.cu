@@ -73,7 +73,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x, true, c)) return;
+  int hh_blk;
+  if (!decode_block(p, 1, true, c, hh_blk)) return;
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -89,7 +90,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = p.head0 + blockIdx.y;
+  const int h = p.head0 + hh_blk;
   const int I = c.idx;
   const int n_tiles = I + 1;
   const int row0 = (int)c.tok0 + I * kBM;
@@ -293,7 +294,7 @@ static cudaError_t launch_fwd_t(const KParams &p, int dtype, cudaStream_t s) {
   auto kernel = tc_fwd_kernel<D, kFp16>;
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D>::kSmem);
   if (e != cudaSuccess) return e;
-  dim3 grid(p.tiles_cap, p.head_cnt);
+  const dim3 grid((unsigned)item_blocks(p, 1));
   kernel<<<grid, kTcThreads, FwdCfg<D>::kSmem, s>>>(mq, mk, mv, p);
   return cudaGetLastError();
 }

@@ -154,7 +154,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x, true, c)) return;
+  int hh_blk;
+  if (!decode_block(p, 1, true, c, hh_blk)) return;
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -171,7 +172,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int hh = hh_blk, h = p.head0 + hh;
   const int I = c.idx;
   const int n_tiles = I + 1;
   const int row0 = (int)c.tok0 + I * kBM;
@@ -320,7 +321,8 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x, false, c)) return;
+  int hh_blk;
+  if (!decode_block(p, 1, false, c, hh_blk)) return;
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -339,7 +341,7 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int hh = hh_blk, h = p.head0 + hh;
   const int J = c.idx;
   const int cnt = c.n_tiles - J;             // query tiles J .. n_tiles-1
   const int krow = (int)c.tok0 + J * kBM;
@@ -551,10 +553,11 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   using namespace dq2;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x, true, c)) return;
-  if (c.idx & 1) return;                        // the block of tiles (idx, idx + 1) belongs to the even tile's CTA
+  int hh_blk;
+  if (!decode_block(p, 2, true, c, hh_blk)) return;   // c.idx: the even tile of the pair (idx, idx + 1)
   const int Ia = c.idx;
   const bool b_active = Ia + 1 < c.n_tiles;
 
@@ -570,7 +573,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int hh = hh_blk, h = p.head0 + hh;
   const int n_sub = (c.len + kBN - 1) / kBN;
   const int steps_a = min(2 * Ia + 2, n_sub);            // sub-tiles 0 .. 2 Ia + 1 reach tile a's diagonal
   const int steps_b = b_active ? min(2 * Ia + 4, n_sub) : 0;
@@ -689,6 +692,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int u = 0; u < my_steps && ok; ++u) {
       ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 530);
       if (!ok) break;
+      if (threadIdx.x == 0 && u == 0) trace_block(p, 1);
       tc_fence_after();
       // the dz tile is still being read by the previous step's dQ MMAs: waited for inside the pass, before its first store
       const uint32_t gate = u >= 1 ? bar(bZEmpty + w) : 0u, gate_parity = (u - 1) & 1;
@@ -728,6 +732,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_block(p, 2);
   if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
@@ -760,9 +765,11 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   using namespace dkv4;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x, false, c)) return;
+  int hh_blk;
+  if (!decode_block(p, 1, false, c, hh_blk)) return;
   const int J = c.idx;                         // the 128-key tile
   const int n_halves = J * kBM + kBN < c.len ? 2 : 1;   // the sequence may end inside the first strip
 
@@ -779,7 +786,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = blockIdx.y, h = p.head0 + hh;
+  const int hh = hh_blk, h = p.head0 + hh;
   const int cnt = c.n_tiles - J;               // query tiles J .. n_tiles-1
   const int n_steps = cnt * n_halves;          // step g: query tile J + g / n_halves, strip g % n_halves
   const int hshift = n_halves - 1;
@@ -908,6 +915,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (g + 1 < n_steps) fetch(g + 1, nr1, ngpre, ndr);
       ok = wait_or_abort(bar(bSpFull + slot), (g >> 1) & 1, abort_flag, p, 630);
       if (!ok) break;
+      if (threadIdx.x == 0 && g == 0) trace_block(p, 1);
       if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, g);
       tc_fence_after();
       const uint32_t tS = tmem + slot * 128 + w * 32 + lane_off, tP = tS + 64;
@@ -975,6 +983,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_block(p, 2);
   if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
@@ -987,7 +996,7 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
   if ((e = make_tile_map(&mk, p.k, p, dtype)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mv, p.v, p, dtype)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mg, p.d_o, p, dtype)) != cudaSuccess) return e;
-  dim3 grid(p.tiles_cap, p.head_cnt);
+  const dim3 grid((unsigned)item_blocks(p, 1)), grid_pairs((unsigned)item_blocks(p, 2));
   CUtensorMap mk64, mv64;   // 64-row boxes for the kernels that stream 64-key sub-tiles
   if (D == 128) {
     if ((e = make_tile_map(&mk64, p.k, p, dtype, 64)) != cudaSuccess) return e;
@@ -997,7 +1006,7 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     auto kernel = tc_bwd_dq2_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq2::kSmem);
     if (e != cudaSuccess) return e;
-    kernel<<<grid, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, p);
+    kernel<<<grid_pairs, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dq) {
     auto kernel = tc_bwd_dq_kernel<D, kFp16>;

@@ -96,9 +96,11 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   using namespace fwd256;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
   TileCoord c;
-  if (!decode_tile(p, blockIdx.x, true, c)) return;   // c.idx: index of the 256-row block inside the sequence
+  int hh_blk;
+  if (!decode_block(p, 1, true, c, hh_blk)) return;   // c.idx: index of the 256-row block inside the sequence
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -114,7 +116,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int tr_cur = 0;   // cursor of this thread's event-log lane (experiments only)
-  const int h = p.head0 + blockIdx.y;
+  const int h = p.head0 + hh_blk;
   const int m = c.idx;
   const int blk_row0 = m * 256;                          // first row of the block inside the sequence
   const int n_sub = (c.len + kBN - 1) / kBN;             // 64-key sub-tiles of the sequence
@@ -233,6 +235,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       ok = wait_or_abort(bar(bSFull + wg * 2 + buf), (u >> 1) & 1, abort_flag, p, 330);
       if (ok && u >= 2) ok = wait_or_abort(bar(bPEmpty + wg * 2 + buf), ((u >> 1) - 1) & 1, abort_flag, p, 331);
       if (!ok) break;
+      if (threadIdx.x == 128 && u == 0) trace_block(p, 1);
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 4 + 16 * wg, t0 + u);
       tc_fence_after();
       const uint32_t ts = tmem + wg * 128 + buf * 64 + lane_off;
@@ -266,6 +269,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace_block(p, 2);
   if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
@@ -275,7 +279,7 @@ cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s) {
   if ((e = make_tile_map(&mq, p.q, p, dtype, kBM)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mk, p.k, p, dtype, fwd256::kBN)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mv, p.v, p, dtype, fwd256::kBN)) != cudaSuccess) return e;
-  dim3 grid(p.tiles_cap, p.head_cnt);
+  const dim3 grid((unsigned)item_blocks(p, 1));
   if (dtype == SB_DTYPE_F16) {
     auto kernel = tc_fwd256_kernel<true>;
     if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
