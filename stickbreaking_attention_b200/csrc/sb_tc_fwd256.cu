@@ -29,8 +29,13 @@ enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bSEmpty = 11, bPFull = 15,
 // per-warpgroup barrier index: base + wg * 2 + buf
 }  // namespace fwd256
 
-// One row, 32 consecutive key columns of a 64-key sub-tile, last column first (see fwd_row_chunk in sb_tc.cu for
-// the recurrence).  key0: index inside the sequence of the sub-tile's column c0; row: index of this query row.
+// One row, 16 consecutive key columns of a 64-key sub-tile, last column first.  key0: index inside the sequence of
+// the chunk's first column; row: index of this query row.
+//   x = z log2(e), clamped at 30;  e = 2^x;  t = 1 + e;  1 - beta = 1 / t;  beta = e / t
+//   p_j = beta_j * (product of (1 - beta) over the allowed keys after j) = e_j * (product of 1 / t over j and after)
+// R carries that product over everything after the current column.  Four columns share one reciprocal and one
+// logarithm of t0 t1 t2 t3; the four inclusive products follow from R, that reciprocal and partial products with
+// five multiplications, and beta itself is never formed.
 template <bool kFp16, bool kMasked>
 __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0, int key0, int row, int ac,
                                                  float scale2, float &R, float &logsum, uint8_t *tile_p, int r) {
@@ -50,25 +55,20 @@ __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0
       if (!(key + 2 < lim)) { e23.x = 0.f; t23.x = 1.f; }
       if (!(key + 3 < lim)) { e23.y = 0.f; t23.y = 1.f; }
     }
-    // one reciprocal and one logarithm for the four factors (1 + e): 1/t_i = (1 / t0 t1 t2 t3) * (product of the others)
-    const float2 pp = mul2(make_float2(t01.x, t23.x), make_float2(t01.y, t23.y));   // (t0 t1, t2 t3)
-    const float prod = pp.x * pp.y;
+    const float p01 = t01.x * t01.y, p23 = t23.x * t23.y;
+    const float prod = p01 * p23;
     const float rp = rcp(prod);
     logsum += lg2(prod);
-    const float2 ab = mul2(make_float2(rp, rp), make_float2(pp.y, pp.x));           // (rp t2 t3, rp t0 t1)
-    const float2 ri01 = mul2(make_float2(ab.x, ab.x), make_float2(t01.y, t01.x));   // (1/t0, 1/t1)
-    const float2 ri23 = mul2(make_float2(ab.y, ab.y), make_float2(t23.y, t23.x));   // (1/t2, 1/t3)
-    const float2 be01 = mul2(e01, ri01), be23 = mul2(e23, ri23);
-    // R after columns 3, 3..2, 3..1 of the group; after all four it is R * rp
-    const float r3 = R * ri23.y;
-    const float2 r21 = mul2(make_float2(r3, r3), make_float2(ri23.x, ri23.x * ri01.y));
-    const float2 p32 = mul2(make_float2(be23.y, be23.x), make_float2(R, r3));
-    const float2 p10 = mul2(make_float2(be01.y, be01.x), r21);
-    pr[4 * g + 3] = p32.x;
-    pr[4 * g + 2] = p32.y;
-    pr[4 * g + 1] = p10.x;
-    pr[4 * g + 0] = p10.y;
-    R *= rp;
+    const float rb = R * (rp * p01);          // R / (t2 t3): inclusive product at column 2
+    const float r3 = rb * t23.x;              // R / t3
+    R *= rp;                                  // R / (t0 t1 t2 t3): at column 0, and the carry into the next group
+    const float r1 = R * t01.x;               // R / (t1 t2 t3)
+    const float2 q01 = mul2(e01, make_float2(R, r1));
+    const float2 q23 = mul2(e23, make_float2(rb, r3));
+    pr[4 * g] = q01.x;
+    pr[4 * g + 1] = q01.y;
+    pr[4 * g + 2] = q23.x;
+    pr[4 * g + 3] = q23.y;
   }
   store_row_chunk16<kFp16>(tile_p, r, c0, pr);
 }
