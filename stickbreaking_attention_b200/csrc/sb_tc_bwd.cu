@@ -14,17 +14,20 @@
 
 namespace sb {
 
-// One row, 16 consecutive key columns starting at c0.  s: raw q.k accumulators, dp: <dO_i, v_j>.
-//   x = z log2(e), clamped at 30;  e = 2^x;  1 - beta = 1 / (1 + e);  beta = e / (1 + e)
+// One row, 16 consecutive key columns.  s: raw q.k accumulators, dp: <dO_i, v_j>.
+//   x = z log2(e), clamped at 30;  e = 2^x;  t = 1 + e;  1 - beta = 1 / t;  beta = e / t
 //   A_j = beta_j * W_j,  W_j = product of (1 - beta) over the allowed keys after j up to the diagonal
+//       = e_j * (product of 1 / t over j and the allowed keys after it)
 //   G = A (dP - dR);  C = gpre + inclusive prefix of G;  dz = G - beta C
-// Three sweeps over the 16 columns, all in registers: (1) e and 1/(1+e) -- four columns share one reciprocal and
-// one logarithm of the product of their (1 + e), which gives the log-space sum through the end of the chunk;
-// (2) last column to first: W is seeded with 2^(r1 + that sum) -- the largest value it takes in the chunk -- and
-// shrinks by (1 - beta) per column, so it only underflows where A rounds to zero anyway; (3) first column to last:
-// the prefix sum of G and dz.  About 1.6 transcendentals per score (ex2, rcp / 4, lg2 / 4, ex2 / 16).
+// Three sweeps over the 16 columns, all in registers: (1) e, beta and, per group of four columns, one reciprocal
+// and one logarithm of t0 t1 t2 t3, which gives the log-space sum through the end of the chunk; (2) last group to
+// first: the product is seeded with 2^(r1 + that sum) -- the largest value it takes in the chunk, so it only
+// underflows where A rounds to zero anyway -- shrinks by the group's reciprocal per group, and the four inclusive
+// products inside a group come from partial reciprocals sweep 1 already has; (3) first group to last: the prefix
+// sum of G, carried per group, and dz.  About 1.6 transcendentals per score (ex2, rcp / 4, lg2 / 4, ex2 / 16).
 // kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
 // The chunk is kept to 16 columns so that the unrolled code of all variants stays inside the instruction cache.
+// mc0: key index of the first column inside the 128-key tile (for the diagonal mask).
 template <bool kMasked>
 __device__ __forceinline__ void bwd_row_chunk_values(const uint32_t (&s)[16], const uint32_t (&dp)[16], int mc0, int r, bool diag,
                                                      int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
@@ -32,57 +35,82 @@ __device__ __forceinline__ void bwd_row_chunk_values(const uint32_t (&s)[16], co
   // columns (tile-local key indices) below `limit` are allowed: one compare per column, no branches
   const int limit = !row_valid ? -1 : (diag ? r + ac : 0x7fffffff);
   const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
-  float be[16], ri[16];
+  float2 e01[4], e23[4], be01[4], be23[4];
+  float rpg[4], q23[4], ri1[4], ri3[4];
 #pragma unroll
   for (int g = 0; g < 4; ++g) {   // independent work in packed pairs (two fp32 per instruction)
     const float2 x01 = mul2(make_float2(__uint_as_float(s[4 * g]), __uint_as_float(s[4 * g + 1])), sc);
     const float2 x23 = mul2(make_float2(__uint_as_float(s[4 * g + 2]), __uint_as_float(s[4 * g + 3])), sc);
-    float2 e01 = make_float2(ex2(fminf(x01.x, 30.f)), ex2(fminf(x01.y, 30.f)));
-    float2 e23 = make_float2(ex2(fminf(x23.x, 30.f)), ex2(fminf(x23.y, 30.f)));
-    float2 t01 = add2(e01, one), t23 = add2(e23, one);
+    e01[g] = make_float2(ex2(fminf(x01.x, 30.f)), ex2(fminf(x01.y, 30.f)));
+    e23[g] = make_float2(ex2(fminf(x23.x, 30.f)), ex2(fminf(x23.y, 30.f)));
+    float2 t01 = add2(e01[g], one), t23 = add2(e23[g], one);
     if (kMasked) {
-      const int col = mc0 + 4 * g;   // mc0: key index inside the 128-key tile (c0 only addresses the output tile)
-      if (!(col < limit)) { e01.x = 0.f; t01.x = 1.f; }
-      if (!(col + 1 < limit)) { e01.y = 0.f; t01.y = 1.f; }
-      if (!(col + 2 < limit)) { e23.x = 0.f; t23.x = 1.f; }
-      if (!(col + 3 < limit)) { e23.y = 0.f; t23.y = 1.f; }
+      const int col = mc0 + 4 * g;
+      if (!(col < limit)) { e01[g].x = 0.f; t01.x = 1.f; }
+      if (!(col + 1 < limit)) { e01[g].y = 0.f; t01.y = 1.f; }
+      if (!(col + 2 < limit)) { e23[g].x = 0.f; t23.x = 1.f; }
+      if (!(col + 3 < limit)) { e23[g].y = 0.f; t23.y = 1.f; }
     }
     const float2 pp = mul2(make_float2(t01.x, t23.x), make_float2(t01.y, t23.y));   // (t0 t1, t2 t3)
     const float prod = pp.x * pp.y;
     const float rp = rcp(prod);
     logsum += lg2(prod);
-    const float2 ab = mul2(make_float2(rp, rp), make_float2(pp.y, pp.x));           // (rp t2 t3, rp t0 t1)
+    const float2 ab = mul2(make_float2(rp, rp), make_float2(pp.y, pp.x));           // (1 / t0 t1, 1 / t2 t3)
     const float2 ri01 = mul2(make_float2(ab.x, ab.x), make_float2(t01.y, t01.x));   // (1/t0, 1/t1)
     const float2 ri23 = mul2(make_float2(ab.y, ab.y), make_float2(t23.y, t23.x));   // (1/t2, 1/t3)
-    const float2 be01 = mul2(e01, ri01), be23 = mul2(e23, ri23);
-    ri[4 * g + 0] = ri01.x; ri[4 * g + 1] = ri01.y; ri[4 * g + 2] = ri23.x; ri[4 * g + 3] = ri23.y;
-    be[4 * g + 0] = be01.x; be[4 * g + 1] = be01.y; be[4 * g + 2] = be23.x; be[4 * g + 3] = be23.y;
+    be01[g] = mul2(e01[g], ri01);
+    be23[g] = mul2(e23[g], ri23);
+    rpg[g] = rp;
+    q23[g] = ab.y;
+    ri1[g] = ri01.y;
+    ri3[g] = ri23.y;
   }
-  float W = ex2(r1 + logsum);
+  float wend = ex2(r1 + logsum);   // product of (1 - beta) over everything after the chunk
 #pragma unroll
-  for (int i = 15; i >= 0; --i) {
-    pa[i] = be[i] * W;
-    W *= ri[i];
+  for (int g = 3; g >= 0; --g) {
+    const float2 w32 = mul2(make_float2(wend, wend), make_float2(ri3[g], q23[g]));   // inclusive products at columns 3, 2
+    const float w1 = w32.y * ri1[g];                                                  // at column 1
+    wend *= rpg[g];                                                                   // at column 0 = after the previous group
+    const float2 a01 = mul2(e01[g], make_float2(wend, w1));
+    const float2 a23 = mul2(e23[g], make_float2(w32.y, w32.x));
+    pa[4 * g] = a01.x;
+    pa[4 * g + 1] = a01.y;
+    pa[4 * g + 2] = a23.x;
+    pa[4 * g + 3] = a23.y;
   }
-  const float2 ndr = make_float2(-dr, -dr), gp = make_float2(gpre, gpre);
+  const float2 ndr = make_float2(-dr, -dr);
+  float cb = gpre + gs, csum = 0.f;   // C before the group; the chunk's own sum of G
 #pragma unroll
-  for (int i = 0; i < 16; i += 2) {
-    float2 g2 = mul2(make_float2(pa[i], pa[i + 1]),
-                     add2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ndr));
+  for (int g = 0; g < 4; ++g) {
+    float2 g01 = mul2(make_float2(pa[4 * g], pa[4 * g + 1]),
+                      add2(make_float2(__uint_as_float(dp[4 * g]), __uint_as_float(dp[4 * g + 1])), ndr));
+    float2 g23 = mul2(make_float2(pa[4 * g + 2], pa[4 * g + 3]),
+                      add2(make_float2(__uint_as_float(dp[4 * g + 2]), __uint_as_float(dp[4 * g + 3])), ndr));
     if (kMasked) {   // rows past the sequence end carry arbitrary values: select, do not rely on 0 * x
-      if (!(mc0 + i < limit)) { g2.x = 0.f; pa[i] = 0.f; }
-      if (!(mc0 + i + 1 < limit)) { g2.y = 0.f; pa[i + 1] = 0.f; }
+      const int col = mc0 + 4 * g;
+      if (!(col < limit)) { g01.x = 0.f; pa[4 * g] = 0.f; }
+      if (!(col + 1 < limit)) { g01.y = 0.f; pa[4 * g + 1] = 0.f; }
+      if (!(col + 2 < limit)) { g23.x = 0.f; pa[4 * g + 2] = 0.f; }
+      if (!(col + 3 < limit)) { g23.y = 0.f; pa[4 * g + 3] = 0.f; }
     }
-    const float gs0 = gs + g2.x;
-    gs = gs0 + g2.y;
-    const float2 z2 = fma2(make_float2(-be[i], -be[i + 1]), add2(make_float2(gs0, gs), gp), g2);
-    pz[i] = z2.x;
-    pz[i + 1] = z2.y;
+    const float t1 = g01.x + g01.y, t23 = g23.x + g23.y;
+    const float tg = t1 + t23;
+    const float c0v = cb + g01.x, c1v = cb + t1;
+    const float c2v = c1v + g23.x;
+    cb += tg;
+    csum += tg;
+    const float2 z01 = fma2(make_float2(-be01[g].x, -be01[g].y), make_float2(c0v, c1v), g01);
+    const float2 z23 = fma2(make_float2(-be23[g].x, -be23[g].y), make_float2(c2v, cb), g23);
+    pz[4 * g] = z01.x;
+    pz[4 * g + 1] = z01.y;
+    pz[4 * g + 2] = z23.x;
+    pz[4 * g + 3] = z23.y;
     if (kMasked) {
-      pz[i] = row_valid ? pz[i] : 0.f;
-      pz[i + 1] = row_valid ? pz[i + 1] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pz[4 * g + i] = row_valid ? pz[4 * g + i] : 0.f;
     }
   }
+  gs += csum;
 }
 
 // The same, written to the 16-bit A (optional) and dz tiles; c0 addresses the output tile.
