@@ -279,6 +279,21 @@ cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p
 // The forward for head sizes above 64 works on 256 query rows per CTA (two 128-row tiles sharing the K/V stream).
 int tc_tile(int head_dim, bool backward) { return (!backward && head_dim > 64) ? 256 : kBM; }
 
+cudaError_t sm_count(int *out) {
+  static int cached[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    cached[dev] = n;
+  }
+  *out = cached[dev];
+  return cudaSuccess;
+}
+
 bool tc_supported(int dtype, int head_dim, bool backward) {
   (void)backward;
   return (dtype == SB_DTYPE_BF16 || dtype == SB_DTYPE_F16) && head_dim % 8 == 0 && head_dim <= 128;

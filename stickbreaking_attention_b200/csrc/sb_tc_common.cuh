@@ -102,6 +102,22 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool
   }
 }
 
+// TMEM accumulator rows (one per thread) -> a 16-bit [128 x D] tile in shared memory (D / 64 blocks of 128-byte
+// rows, 128-byte swizzle), from where TMA stores it with full lines instead of 16 bytes per thread and row.
+template <int D, bool kFp16>
+__device__ __forceinline__ void stage_acc_rows(uint32_t tmem_addr, uint8_t *tile, int r, float mul) {
+#pragma unroll 1
+  for (int ch = 0; ch < D / 32; ++ch) {
+    uint32_t v[32];
+    tmem_ld32(tmem_addr + ch * 32, v);
+    tmem_wait_ld();
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]) * mul;
+    store_row_chunk<kFp16>(tile, r, ch * 32, x);
+  }
+}
+
 // MMA issue helpers (called by one thread).  The issuing thread is a scalar instruction stream, so descriptors are
 // built once per tile and only their 14-bit start-address field (bytes >> 4) is advanced per instruction:
 // a K-major operand moves 32 bytes per 16-element K step inside a 64-element block and one box per block; an

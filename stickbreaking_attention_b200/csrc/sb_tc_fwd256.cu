@@ -25,7 +25,7 @@ constexpr int kStageBytes = 2 * kKvTileBytes; // K and V
 constexpr int kPBytes = kBM * kBN * 2;        // one P buffer: 128 rows x 64 keys
 constexpr int kBarBytes = 512;
 constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
-enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bSEmpty = 11, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 24 };
+enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bQFree = 11, bOFree = 12, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 24 };
 // per-warpgroup barrier index: base + wg * 2 + buf
 }  // namespace fwd256
 
@@ -89,18 +89,50 @@ __device__ __forceinline__ void fwd256_row_pass(uint32_t ts, int key0, int row, 
   }
 }
 
+// What one work item (a 256-row block of one sequence and head) looks like to every role.
+struct Fwd256Item {
+  TileCoord c;
+  int h;          // head
+  int blk_row0;   // first row of the block inside the sequence
+  bool b_active;  // the block has a second tile
+  int s_top;      // sub-tile of step 0; step t handles sub-tile s_top - t
+  int n_steps;
+  int t0_a;       // first step in which tile a takes part
+};
+
+// Item number `it` of this block: the launch holds one block per SM; blocks walk the weight-ordered item list in a
+// boustrophedon (even rounds left to right, odd rounds right to left), which evens out the sums of the weights.
+__device__ __forceinline__ bool fwd256_item(const KParams &p, int it, Fwd256Item &w) {
+  const long long G = gridDim.x;
+  const long long lin = (long long)it * G + ((it & 1) ? G - 1 - blockIdx.x : blockIdx.x);
+  const long long item = lin / p.head_cnt;
+  if (item > 0x7fffffffLL || !decode_item(p, (int)item, 1, true, w.c)) return false;
+  w.h = p.head0 + (int)(lin - item * p.head_cnt);
+  const int m = w.c.idx;
+  const int n_sub = (w.c.len + fwd256::kBN - 1) / fwd256::kBN;   // 64-key sub-tiles of the sequence
+  w.blk_row0 = m * 256;
+  w.b_active = w.blk_row0 + kBM < w.c.len;
+  const int s_hi_a = min(4 * m + 1, n_sub - 1);                 // last sub-tile tile a needs
+  const int s_hi_b = min(4 * m + 3, n_sub - 1);
+  w.s_top = w.b_active ? s_hi_b : s_hi_a;
+  w.n_steps = w.s_top + 1;
+  w.t0_a = w.s_top - s_hi_a;
+  return true;
+}
+
+// Persistent: every block works through several items; all barrier phases run on across items (the counters T, U
+// below), so the loads and first MMAs of the next item overlap the last row pass and the epilogue of the current one.
+// Per item and role the barriers advance by fixed amounts whether or not tile b exists: an idle issuer still commits
+// and releases the K/V stages (after they were filled, so that it cannot run ahead of a phase).
 template <bool kFp16>
 __global__ void __launch_bounds__(fwd256::kThreads, 1)
 tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const KParams p) {
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const KParams p) {
   using namespace fwd256;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
-  TileCoord c;
-  int hh_blk;
-  if (!decode_block(p, 1, true, c, hh_blk)) return;   // c.idx: index of the 256-row block inside the sequence
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -116,27 +148,19 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int tr_cur = 0;   // cursor of this thread's event-log lane (experiments only)
-  const int h = p.head0 + hh_blk;
-  const int m = c.idx;
-  const int blk_row0 = m * 256;                          // first row of the block inside the sequence
-  const int n_sub = (c.len + kBN - 1) / kBN;             // 64-key sub-tiles of the sequence
-  const bool b_active = blk_row0 + kBM < c.len;
-  const int s_hi_a = min(4 * m + 1, n_sub - 1);          // last sub-tile tile a needs
-  const int s_hi_b = min(4 * m + 3, n_sub - 1);
-  const int s_top = b_active ? s_hi_b : s_hi_a;
-  const int n_steps = s_top + 1;                         // step t handles sub-tile s_top - t
-  const int t0_a = s_top - s_hi_a;                       // first step in which tile a takes part
 
   if (threadIdx.x == 0) {
     mbar_init(bar(bQ), 1);
-    const int issuers = b_active ? 2 : 1;   // both MMA issuers release a K/V stage and signal the end
-    for (int s = 0; s < kStages; ++s) { mbar_init(bar(bKvFull + s), 1); mbar_init(bar(bKvEmpty + s), issuers); }
+    mbar_init(bar(bQFree), 2);
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar(bKvFull + s), 1); mbar_init(bar(bKvEmpty + s), 2); }
     for (int s = 0; s < 4; ++s) {
       mbar_init(bar(bSFull + s), 1);
       mbar_init(bar(bPFull + s), 4);
       mbar_init(bar(bPEmpty + s), 1);
     }
-    mbar_init(bar(bOFull), issuers);
+    mbar_init(bar(bOFull), 2);
+    mbar_init(bar(bOFree), 4);
+    mbar_init(bar(bOFree + 1), 4);
     ctl->abort = 0;
     fence_barrier_init();
   }
@@ -149,71 +173,96 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
 
+  Fwd256Item w;
   if (warp == 8) {
     // ------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
-      const int qrow = (int)c.tok0 + blk_row0;
-      mbar_arrive_expect_tx(bar(bQ), 2 * kQBytes);
-      for (int t = 0; t < 2; ++t)
-        for (int kb = 0; kb < 2; ++kb)
-          tma_load_4d(sQ + t * kQBytes + kb * kBoxBytes, &tm_q, bar(bQ), kb * 64, qrow + t * kBM, h, (int)c.boff);
-      for (int t = 0; t < n_steps; ++t) {
-        const int st = t % kStages;
-        if (t >= kStages && !wait_or_abort(bar(bKvEmpty + st), ((t / kStages) - 1) & 1, abort_flag, p, 310)) break;
-        if (*abort_flag) break;
-        const int krow = (int)c.tok0 + (s_top - t) * kBN;
-        const uint32_t dst = sKV + st * kStageBytes;
-        trace_event(p, 0, tr_cur, 1, t);
-        mbar_arrive_expect_tx(bar(bKvFull + st), kStageBytes);
-        for (int kb = 0; kb < 2; ++kb) {
-          tma_load_4d(dst + kb * kKvBoxBytes, &tm_k, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
-          tma_load_4d(dst + kKvTileBytes + kb * kKvBoxBytes, &tm_v, bar(bKvFull + st), kb * 64, krow, h, (int)c.boff);
+      int T = 0;   // K/V stages filled so far
+      for (int it = 0; fwd256_item(p, it, w); ++it) {
+        // Q of the previous item is no longer read once both issuers have finished its last S MMAs
+        if (it >= 1 && !wait_or_abort(bar(bQFree), (it - 1) & 1, abort_flag, p, 311)) break;
+        const int qrow = (int)w.c.tok0 + w.blk_row0;
+        mbar_arrive_expect_tx(bar(bQ), 2 * kQBytes);
+        for (int t = 0; t < 2; ++t)
+          for (int kb = 0; kb < 2; ++kb)
+            tma_load_4d(sQ + t * kQBytes + kb * kBoxBytes, &tm_q, bar(bQ), kb * 64, qrow + t * kBM, w.h, (int)w.c.boff);
+        bool ok = true;
+        for (int t = 0; t < w.n_steps; ++t) {
+          const int g = T + t, st = g % kStages;
+          if (g >= kStages && !wait_or_abort(bar(bKvEmpty + st), ((g / kStages) - 1) & 1, abort_flag, p, 310)) { ok = false; break; }
+          if (*abort_flag) { ok = false; break; }
+          const int krow = (int)w.c.tok0 + (w.s_top - t) * kBN;
+          const uint32_t dst = sKV + st * kStageBytes;
+          trace_event(p, 0, tr_cur, 1, t);
+          mbar_arrive_expect_tx(bar(bKvFull + st), kStageBytes);
+          for (int kb = 0; kb < 2; ++kb) {
+            tma_load_4d(dst + kb * kKvBoxBytes, &tm_k, bar(bKvFull + st), kb * 64, krow, w.h, (int)w.c.boff);
+            tma_load_4d(dst + kKvTileBytes + kb * kKvBoxBytes, &tm_v, bar(bKvFull + st), kb * 64, krow, w.h, (int)w.c.boff);
+          }
         }
+        if (!ok) break;
+        T += w.n_steps;
       }
     }
   } else if (warp >= 9) {
     // ------------------------------------------------ MMA issuers: warp 9 for tile a, warp 10 for tile b
     const int wg = warp - 9;
-    if (lane == 0 && (wg == 0 || b_active)) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(kBM, D, kFp16, false, true);
-      const int t0 = wg == 0 ? t0_a : 0;
-      const int my_steps = n_steps - t0;
       const uint32_t qaddr = sQ + wg * kQBytes;
-      // tile a does not read the first t0_a stages: release them on its behalf
-      for (int t = 0; t < t0; ++t) mbar_arrive(bar(bKvEmpty + t % kStages));
-      bool ok = wait_or_abort(bar(bQ), 0, abort_flag, p, 320);
-      // Iteration u issues S(u) and then P V of step u-1, so that the next scores are being computed while the
-      // rows of the current step are processed.  S(u) reuses the TMEM slot of step u-2, whose rows were finished
-      // before p_full(u-2) was signalled, and that was waited for in iteration u-1.
-      for (int u = 0; ok && u <= my_steps; ++u) {
-        if (u < my_steps) {
-          const int t = t0 + u, st = t % kStages;
-          ok = wait_or_abort(bar(bKvFull + st), (t / kStages) & 1, abort_flag, p, 321);
-          if (!ok) break;
-          trace_event(p, 1 + 3 * wg, tr_cur, 2 + 16 * wg, t);
-          tc_fence_after();
-          mma_kmajor_kmajor<D, kBoxBytes, kKvBoxBytes>(tmem + wg * 128 + (u & 1) * 64, qaddr, sKV + st * kStageBytes, idesc_s,
-                                                       false);
-          mma_commit(bar(bSFull + wg * 2 + (u & 1)));
-          trace_event(p, 1 + 3 * wg, tr_cur, 3 + 16 * wg, t);
+      int T = 0, U = 0;   // K/V stages and this tile's steps of the earlier items
+      bool ok = true;
+      for (int it = 0; ok && fwd256_item(p, it, w); ++it) {
+        const bool active = wg == 0 || w.b_active;
+        const int t0 = active ? (wg == 0 ? w.t0_a : 0) : w.n_steps;   // stages this tile does not read
+        const int my_steps = w.n_steps - t0;
+        // release the unread stages on this tile's behalf, each once it has been filled
+        for (int t = 0; ok && t < t0; ++t) {
+          const int g = T + t;
+          ok = wait_or_abort(bar(bKvFull + g % kStages), (g / kStages) & 1, abort_flag, p, 324);
+          if (ok) mbar_arrive(bar(bKvEmpty + g % kStages));
         }
-        if (u >= 1) {
-          const int up = u - 1, t = t0 + up, st = t % kStages;
-          ok = wait_or_abort(bar(bPFull + wg * 2 + (up & 1)), (up >> 1) & 1, abort_flag, p, 323);
-          if (!ok) break;
-          trace_event(p, 1 + 3 * wg, tr_cur, 6 + 16 * wg, t);
-          tc_fence_after();
-          // 16 keys per MMA; V: 64 rows x (2 x 64) columns, MN-major
-          mma_kmajor_mnmajor<kBN, kKvBoxBytes>(tmem + 256 + wg * 128, sP + (wg * 2 + (up & 1)) * kPBytes,
-                                               sKV + st * kStageBytes + kKvTileBytes, idesc_pv, up > 0);
-          mma_commit(bar(bPEmpty + wg * 2 + (up & 1)));
-          mma_commit(bar(bKvEmpty + st));
-          trace_event(p, 1 + 3 * wg, tr_cur, 7 + 16 * wg, t);
+        if (ok && active) ok = wait_or_abort(bar(bQ), it & 1, abort_flag, p, 320);
+        // Iteration u issues S(u) and then P V of step u-1, so that the next scores are being computed while the
+        // rows of the current step are processed.  S(u) reuses the TMEM slot of step u-2, whose rows were finished
+        // before p_full(u-2) was signalled, and that was waited for in iteration u-1.
+        for (int u = 0; ok && active && u <= my_steps; ++u) {
+          if (u < my_steps) {
+            const int g = T + t0 + u, st = g % kStages, gu = U + u;
+            ok = wait_or_abort(bar(bKvFull + st), (g / kStages) & 1, abort_flag, p, 321);
+            if (!ok) break;
+            trace_event(p, 1 + 3 * wg, tr_cur, 2 + 16 * wg, t0 + u);
+            tc_fence_after();
+            mma_kmajor_kmajor<D, kBoxBytes, kKvBoxBytes>(tmem + wg * 128 + (gu & 1) * 64, qaddr, sKV + st * kStageBytes, idesc_s,
+                                                         false);
+            mma_commit(bar(bSFull + wg * 2 + (gu & 1)));
+            if (u == my_steps - 1) mma_commit(bar(bQFree));   // the item's last read of Q
+            trace_event(p, 1 + 3 * wg, tr_cur, 3 + 16 * wg, t0 + u);
+          }
+          if (u >= 1) {
+            const int up = u - 1, g = T + t0 + up, st = g % kStages, gu = U + up;
+            ok = wait_or_abort(bar(bPFull + wg * 2 + (gu & 1)), (gu >> 1) & 1, abort_flag, p, 323);
+            // the accumulator still holds the previous item's O until its rows have read it
+            if (ok && up == 0 && it >= 1) ok = wait_or_abort(bar(bOFree + wg), (it - 1) & 1, abort_flag, p, 325);
+            if (!ok) break;
+            trace_event(p, 1 + 3 * wg, tr_cur, 6 + 16 * wg, t0 + up);
+            tc_fence_after();
+            // 16 keys per MMA; V: 64 rows x (2 x 64) columns, MN-major
+            mma_kmajor_mnmajor<kBN, kKvBoxBytes>(tmem + 256 + wg * 128, sP + (wg * 2 + (gu & 1)) * kPBytes,
+                                                 sKV + st * kStageBytes + kKvTileBytes, idesc_pv, up > 0);
+            mma_commit(bar(bPEmpty + wg * 2 + (gu & 1)));
+            mma_commit(bar(bKvEmpty + st));
+            trace_event(p, 1 + 3 * wg, tr_cur, 7 + 16 * wg, t0 + up);
+          }
         }
+        if (!ok) break;
+        if (!active) mma_commit(bar(bQFree));   // after this thread's earlier MMAs, like every arrival on these two
+        mma_commit(bar(bOFull));
+        T += w.n_steps;
+        U += my_steps;
       }
-      if (ok) mma_commit(bar(bOFull));
     }
   } else {
     // ------------------------------------------------ one thread per query row, one warpgroup per 128-row tile
@@ -223,48 +272,80 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float scale2 = p.scale * kLog2e;
     const int ac = p.attend_current;
-    const int row = blk_row0 + wg * kBM + r;         // row index inside the sequence
-    const int t0 = wg == 0 ? t0_a : 0;
-    const int my_steps = (wg == 1 && !b_active) ? 0 : n_steps - t0;
-    const int s_diag0 = 4 * m + 2 * wg;              // first sub-tile that reaches this tile's diagonal band
-    double run = 0.0;
+    int U = 0;
     bool ok = true;
-    for (int u = 0; u < my_steps && ok; ++u) {
-      const int s = s_top - (t0 + u);
-      const int buf = u & 1;
-      ok = wait_or_abort(bar(bSFull + wg * 2 + buf), (u >> 1) & 1, abort_flag, p, 330);
-      if (ok && u >= 2) ok = wait_or_abort(bar(bPEmpty + wg * 2 + buf), ((u >> 1) - 1) & 1, abort_flag, p, 331);
-      if (!ok) break;
-      if (threadIdx.x == 128 && u == 0) trace_block(p, 1);
-      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 4 + 16 * wg, t0 + u);
-      tc_fence_after();
-      const uint32_t ts = tmem + wg * 128 + buf * 64 + lane_off;
-      uint8_t *tile_p = gP + (wg * 2 + buf) * kPBytes;
-      float R = ex2(-(float)run);
-      float logsum = 0.f;
-      // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
-      if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r);
-      else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r);
-      run += (double)logsum;
-      tc_fence_before();          // this step's TMEM reads are done before the slot is handed back
-      fence_proxy_async_smem();
+    for (int it = 0; ok && fwd256_item(p, it, w); ++it) {
+      const bool active = wg == 0 || w.b_active;
+      const int t0 = wg == 0 ? w.t0_a : 0;
+      const int my_steps = active ? w.n_steps - t0 : 0;
+      const int row = w.blk_row0 + wg * kBM + r;       // row index inside the sequence
+      const int s_diag0 = 4 * w.c.idx + 2 * wg;        // first sub-tile that reaches this tile's diagonal band
+      double run = 0.0;
+      if (lane == 0) tma_store_wait_read();   // the previous item's O has left the P buffers
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(bPFull + wg * 2 + buf));
-      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 5 + 16 * wg, t0 + u);
-    }
-    // ---- epilogue: O (TMEM) -> global, rem, log_rem
-    if (ok && my_steps > 0) ok = wait_or_abort(bar(bOFull), 0, abort_flag, p, 332);
-    if (ok && my_steps > 0) {
-      tc_fence_after();
-      const bool valid = row < c.len;
-      T *orow = reinterpret_cast<T *>(p.o.ptr) + c.boff * p.o.sb + (long long)h * p.o.sh + (c.tok0 + row) * p.o.st;
-      store_acc_rows<D, kFp16, T>(tmem + 256 + wg * 128 + lane_off, orow, valid, p.head_dim, 1.f);
-      if (valid) {
-        const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + row;
-        reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(ex2(-(float)run));
-        p.log_rem[idx] = -run;
+      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 40 + wg, it);
+      for (int u = 0; u < my_steps && ok; ++u) {
+        const int s = w.s_top - (t0 + u);
+        const int gu = U + u, buf = gu & 1;
+        ok = wait_or_abort(bar(bSFull + wg * 2 + buf), (gu >> 1) & 1, abort_flag, p, 330);
+        if (ok && gu >= 2) ok = wait_or_abort(bar(bPEmpty + wg * 2 + buf), ((gu >> 1) - 1) & 1, abort_flag, p, 331);
+        if (!ok) break;
+        if (threadIdx.x == 128 && u == 0 && it == 0) trace_block(p, 1);
+        if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 4 + 16 * wg, t0 + u);
+        tc_fence_after();
+        const uint32_t ts = tmem + wg * 128 + buf * 64 + lane_off;
+        uint8_t *tile_p = gP + (wg * 2 + buf) * kPBytes;
+        float R = ex2(-(float)run);
+        float logsum = 0.f;
+        // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
+        if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r);
+        else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r);
+        run += (double)logsum;
+        tc_fence_before();          // this step's TMEM reads are done before the slot is handed back
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(bPFull + wg * 2 + buf));
+        if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 5 + 16 * wg, t0 + u);
       }
+      // ---- epilogue: O (TMEM) -> global, rem, log_rem
+      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 42 + wg, it);
+      if (ok) ok = wait_or_abort(bar(bOFull), it & 1, abort_flag, p, 332);
+      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 44 + wg, it);
+      if (ok && my_steps > 0) {
+        tc_fence_after();
+        const bool valid = row < w.c.len;
+        const int tile_row0 = w.blk_row0 + wg * kBM;
+        if (tile_row0 + kBM <= w.c.len) {
+          // full tile: through this tile's two P buffers (all P V MMAs are done), one TMA store per warp and half
+          uint8_t *stage = gP + wg * 2 * kPBytes;
+          stage_acc_rows<D, kFp16>(tmem + 256 + wg * 128 + lane_off, stage, r, 1.f);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t src = sP + wg * 2 * kPBytes + (warp & 3) * 32 * 128;
+            const int trow = (int)w.c.tok0 + tile_row0 + (warp & 3) * 32;
+            tma_store_4d(&tm_o, src, 0, trow, w.h, (int)w.c.boff);
+            tma_store_4d(&tm_o, src + kPBytes, 64, trow, w.h, (int)w.c.boff);
+            tma_store_commit();
+          }
+        } else {
+          // the sequence ends inside the tile: row by row, rows past the end are left alone
+          T *orow = reinterpret_cast<T *>(p.o.ptr) + w.c.boff * p.o.sb + (long long)w.h * p.o.sh + (w.c.tok0 + row) * p.o.st;
+          store_acc_rows<D, kFp16, T>(tmem + 256 + wg * 128 + lane_off, orow, valid, p.head_dim, 1.f);
+        }
+        if (valid) {
+          const long long idx = (w.c.boff * p.heads + w.h) * p.tokens + w.c.tok0 + row;
+          reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(ex2(-(float)run));
+          p.log_rem[idx] = -run;
+        }
+      }
+      tc_fence_before();            // the accumulator has been read: the next item may overwrite it
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bOFree + wg));
+      if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 46 + wg, it);
+      U += my_steps;
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -274,20 +355,24 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s) {
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   cudaError_t e;
   if ((e = make_tile_map(&mq, p.q, p, dtype, kBM)) != cudaSuccess) return e;
+  if ((e = make_tile_map(&mo, p.o, p, dtype, 32)) != cudaSuccess) return e;   // stores: 32 rows per warp
   if ((e = make_tile_map(&mk, p.k, p, dtype, fwd256::kBN)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mv, p.v, p, dtype, fwd256::kBN)) != cudaSuccess) return e;
-  const dim3 grid((unsigned)item_blocks(p, 1));
+  int sms = 0;
+  if ((e = sm_count(&sms)) != cudaSuccess) return e;
+  const long long blocks = item_blocks(p, 1);
+  const dim3 grid((unsigned)(blocks < sms ? blocks : sms));   // one resident block per SM
   if (dtype == SB_DTYPE_F16) {
     auto kernel = tc_fwd256_kernel<true>;
     if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
-    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, p);
+    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, mo, p);
   } else {
     auto kernel = tc_fwd256_kernel<false>;
     if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
-    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, p);
+    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, mo, p);
   }
   return cudaGetLastError();
 }
