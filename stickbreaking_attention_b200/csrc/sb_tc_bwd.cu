@@ -577,7 +577,8 @@ enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9,
 template <bool kFp16>
 __global__ void __launch_bounds__(dq2::kThreads, 1)
 tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
+                  const __grid_constant__ CUtensorMap tm_dq, const KParams p) {
   using namespace dq2;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
@@ -753,8 +754,39 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (ok && my_steps > 0) ok = wait_or_abort(bar(bDqFull), 0, abort_flag, p, 532);
     if (ok && my_steps > 0) {
       tc_fence_after();
-      T *grow = reinterpret_cast<T *>(p.dq.ptr) + c.boff * p.dq.sb + (long long)h * p.dq.sh + (c.tok0 + gi) * p.dq.st;
-      store_acc_rows<D, kFp16, T>(tmem + 256 + w * 128 + lane_off, grow, valid, p.head_dim, p.scale);
+      const uint32_t t_acc = tmem + 256 + w * 128 + lane_off;
+      if (I * kBM + kBM <= c.len) {
+        // full tile: two 64-column halves through this tile's dz buffer (its last dQ MMA is done), one TMA store per
+        // warp and half -- full lines instead of 16 bytes per thread and row
+        const uint32_t src = sZ + w * kZBytes + (warp & 3) * 32 * 128;
+        const int trow = (int)c.tok0 + I * kBM + (warp & 3) * 32;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t v[32];
+            tmem_ld32(t_acc + half * 64 + ch * 32, v);
+            tmem_wait_ld();
+            float x[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]) * p.scale;
+            store_row_chunk<kFp16>(gZ, r, ch * 32, x);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&tm_dq, src, half * 64, trow, h, (int)c.boff);
+            tma_store_commit();
+            tma_store_wait_read();   // the buffer is rewritten by the next half
+          }
+          __syncwarp();
+        }
+        if (lane == 0) tma_store_wait_all();
+      } else {
+        // the sequence ends inside the tile: row by row, rows past the end are left alone
+        T *grow = reinterpret_cast<T *>(p.dq.ptr) + c.boff * p.dq.sb + (long long)h * p.dq.sh + (c.tok0 + gi) * p.dq.st;
+        store_acc_rows<D, kFp16, T>(t_acc, grow, valid, p.head_dim, p.scale);
+      }
     }
   }
 
@@ -783,13 +815,15 @@ constexpr int kTileBytes = kBM * 128 * 2;      // Q, dO, K or V tile: two 128 x 
 constexpr int kStripOffset = kBN * 128;        // byte offset of strip 1 inside a box (64 rows of 128 bytes)
 constexpr int kAzBytes = kBM * kBN * 2;        // A or dz tile, 128 rows x 64 keys
 constexpr int kSmem = 1024 + 2 * kTileBytes + 4 * kTileBytes + 2 * kAzBytes + 512;
-enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bSpEmpty = 7, bAzFull = 9, bAzEmpty = 10, bOutFull = 11, bNum = 12 };
+enum { bKV = 0, bQgFull = 1, bQgEmpty = 3, bSpFull = 5, bSpEmpty = 7, bAzFull = 9, bAzEmpty = 10, bOutFull = 11, bStaged = 12,
+       bDrained = 14, bNum = 16 };
 }  // namespace dkv4
 
 template <bool kFp16>
 __global__ void __launch_bounds__(dkv4::kThreads, 1)
 tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
+                   const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, const KParams p) {
   using namespace dkv4;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
@@ -831,6 +865,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_init(bar(bAzFull), 8);
     mbar_init(bar(bAzEmpty), 1);
     mbar_init(bar(bOutFull), 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(bar(bStaged + b), 4); mbar_init(bar(bDrained + b), 1); }
     ctl->abort = 0;
     fence_barrier_init();
   }
@@ -984,28 +1019,62 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (lane == 0) mbar_arrive(bar(bAzFull));
       if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, g);
     }
-    // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys
+    // ---- epilogue: dK^T (warps 0-3) and dV^T (warps 4-7), lanes = head dimension, columns = keys.  A full strip is
+    // transposed into this warpgroup's buffer (A for dK, dz for dV: all their MMAs are done) and leaves by TMA;
+    // a strip the sequence ends in is written element by element.
     if (ok) ok = wait_or_abort(bar(bOutFull), 0, abort_flag, p, 632);
     if (ok) {
       tc_fence_after();
       const TensorRef &out = w == 0 ? p.dk : p.dv;
+      const CUtensorMap *omap = w == 0 ? &tm_dk : &tm_dv;
       const float mul = w == 0 ? p.scale : 1.f;
+      uint8_t *stage = w == 0 ? gA : gZ;
+      const uint32_t stage_addr = sAZ + w * kAzBytes;
       T *obase = reinterpret_cast<T *>(out.ptr) + c.boff * out.sb + (long long)h * out.sh + (c.tok0 + J * kBM) * out.st + r;
+      int round = 0;
 #pragma unroll 1
-      for (int ch = 0; ch < 4 * n_halves; ++ch) {
-        // 16 keys per load: strip ch / 4, columns (ch % 4) * 16 of this warpgroup's accumulator
-        const uint32_t t_acc = tmem + 256 + (ch >> 2) * 128 + w * 64 + (ch & 3) * 16 + lane_off;
-        uint32_t va[16];
-        tmem_ld16(t_acc, va);
-        tmem_wait_ld();
-        if (r < p.head_dim) {
+      for (int hf = 0; hf < n_halves && ok; ++hf) {
+        const bool full = J * kBM + hf * kBN + kBN <= c.len && p.head_dim == D;   // the same for all row warps
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t va[16];
+          tmem_ld16(tmem + 256 + hf * 128 + w * 64 + ch * 16 + lane_off, va);
+          tmem_wait_ld();
+          if (full) {
+            // element (key, r) of a [64 keys x 128] tile: two 64-column blocks, 128-byte swizzle
+            const uint32_t col_off = (r >> 6) * (kBN * 128) + (r & 7) * 2;
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const int key = J * kBM + ch * 16 + k;
-            if (key < c.len) obase[(long long)(ch * 16 + k) * out.st] = from_f32<T>(__uint_as_float(va[k]) * mul);
+            for (int k = 0; k < 16; ++k) {
+              const int key = ch * 16 + k;
+              const uint32_t off = col_off + (key >> 3) * 1024 + (key & 7) * 128 + ((((r & 63) >> 3) ^ (key & 7)) << 4);
+              *reinterpret_cast<T *>(stage + off) = from_f32<T>(__uint_as_float(va[k]) * mul);
+            }
+          } else if (r < p.head_dim) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              const int key = J * kBM + hf * kBN + ch * 16 + k;
+              if (key < c.len) obase[(long long)(hf * kBN + ch * 16 + k) * out.st] = from_f32<T>(__uint_as_float(va[k]) * mul);
+            }
           }
         }
+        if (full) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(bStaged + w));
+          if (r == 0 && (ok = wait_or_abort(bar(bStaged + w), round & 1, abort_flag, p, 633))) {
+            const int krow = (int)c.tok0 + J * kBM + hf * kBN;
+            tma_store_4d(omap, stage_addr, 0, krow, h, (int)c.boff);
+            tma_store_4d(omap, stage_addr + kBN * 128, 64, krow, h, (int)c.boff);
+            tma_store_commit();
+            tma_store_wait_read();
+            mbar_arrive(bar(bDrained + w));
+          }
+          // the buffer is rewritten for the next strip
+          if (ok && hf + 1 < n_halves) ok = wait_or_abort(bar(bDrained + w), round & 1, abort_flag, p, 634);
+          ++round;
+        }
       }
+      if (r == 0) tma_store_wait_all();
     }
   }
 
@@ -1034,7 +1103,9 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     auto kernel = tc_bwd_dq2_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq2::kSmem);
     if (e != cudaSuccess) return e;
-    kernel<<<grid_pairs, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, p);
+    CUtensorMap mdq;   // stores: 32 rows per warp
+    if ((e = make_tile_map(&mdq, p.dq, p, dtype, 32)) != cudaSuccess) return e;
+    kernel<<<grid_pairs, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, mdq, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dq) {
     auto kernel = tc_bwd_dq_kernel<D, kFp16>;
@@ -1047,7 +1118,10 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     auto kernel = tc_bwd_dkv4_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv4::kSmem);
     if (e != cudaSuccess) return e;
-    kernel<<<grid, dkv4::kThreads, dkv4::kSmem, s>>>(mq, mk, mv, mg, p);
+    CUtensorMap mdk, mdv;   // stores: one 64-key strip at a time
+    if ((e = make_tile_map(&mdk, p.dk, p, dtype, 64)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mdv, p.dv, p, dtype, 64)) != cudaSuccess) return e;
+    kernel<<<grid, dkv4::kThreads, dkv4::kSmem, s>>>(mq, mk, mv, mg, mdk, mdv, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dkv) {
     auto kernel = tc_bwd_dkv_kernel<D, kFp16>;
