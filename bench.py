@@ -13,7 +13,8 @@ the algorithmic FLOPs divided by the slowest rank's device time.
 Printed by rank 0, one JSON line:
   value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks
   e2e        same metric through the public Python operator with pinned HOST buffers: the H2D copies of
-             q, k, v, dO, dRem and the D2H copies of o, rem, dq, dk, dv are inside the timed region
+             q, k, v, dO, dRem and the D2H copies of o, rem, dq, dk, dv are inside the timed region (every step
+             copies all of them; the copies of neighbouring steps overlap the compute on separate streams)
   roofline   the dominant kernel against the measured dense bf16 tensor peak
   cpu_baseline  the CPU oracle (a port of the reference's sb_ref) on a bounded sample, rank 0, N == 1
 
@@ -300,19 +301,47 @@ def run_gpu_arm(args, w):
         return torch.autograd.grad((o, rem), (q, k, v), (dev_t["do"], dev_t["drem"]))
 
     out_host = {}
+    # End to end, as a training loop would drive it: three streams and two sets of device input buffers, so that the
+    # host->device copy of step i+1 and the device->host copy of step i-1 run while step i computes.  Every step still
+    # copies all of its inputs from pinned host memory and all of its results back, inside the timed region.
+    s_in, s_cmp, s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+    dev_in = [{n: torch.empty_like(t, device=device) for n, t in host.items()} for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    for ev in in_free:
+        ev.record()
+    e2e_state = {"i": 0}
 
     def step_e2e():
-        q, k, v, do, drem = (host[n].to(device, non_blocking=True) for n in ("q", "k", "v", "do", "drem"))
-        q, k, v = (t.requires_grad_(not fwd_only) for t in (q, k, v))
-        o, rem = sb.sb_attn_varlen(q, k, v, cu, max_len, zero_start=w["zero_start"])
-        results = {"o": o, "rem": rem}
-        if not fwd_only:
-            dq, dk, dv = torch.autograd.grad((o, rem), (q, k, v), (do, drem))
-            results.update(dq=dq, dk=dk, dv=dv)
-        for name, t in results.items():
-            if name not in out_host:
-                out_host[name] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
-            out_host[name].copy_(t.detach(), non_blocking=True)
+        b = e2e_state["i"] % 2
+        e2e_state["i"] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[b])          # the step that last used this buffer set has finished with it
+            for n, t in host.items():
+                dev_in[b][n].copy_(t, non_blocking=True)
+            in_ready[b].record(s_in)
+        with torch.cuda.stream(s_cmp):
+            s_cmp.wait_event(in_ready[b])
+            q, k, v = (dev_in[b][n].detach().requires_grad_(not fwd_only) for n in ("q", "k", "v"))
+            o, rem = sb.sb_attn_varlen(q, k, v, cu, max_len, zero_start=w["zero_start"])
+            results = {"o": o, "rem": rem}
+            if not fwd_only:
+                dq, dk, dv = torch.autograd.grad((o, rem), (q, k, v), (dev_in[b]["do"], dev_in[b]["drem"]))
+                results.update(dq=dq, dk=dk, dv=dv)
+            in_free[b].record(s_cmp)
+            done = torch.cuda.Event()
+            done.record(s_cmp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            for name, t in results.items():
+                t = t.detach()
+                if name not in out_host:
+                    out_host[name] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                t.record_stream(s_out)
+                out_host[name].copy_(t, non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record(s_out)
+        torch.cuda.current_stream().wait_event(copied)   # the timing events sit on the current stream
 
     def barrier():
         if distributed:
@@ -381,7 +410,8 @@ def run_gpu_arm(args, w):
                        "flop_convention": "causal: fwd 2*L^2*d per head per sequence, bwd 2.5x"},
             "tokens_per_s": sum(w["lengths"]) * world / (ms_step * 1e-3),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e, "steps": e2e_steps},
+                    "ms_per_step": ms_e2e, "steps": e2e_steps,
+                    "overlap": "h2d of step i+1 and d2h of step i-1 run on their own streams while step i computes"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roofline,
