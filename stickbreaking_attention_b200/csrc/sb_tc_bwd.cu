@@ -571,7 +571,7 @@ constexpr int kKvTile = 2 * kKvBox;            // K or V sub-tile
 constexpr int kStageBytes = 2 * kKvTile;
 constexpr int kZBytes = kBM * kBN * 2;         // dz tile: 128 rows x 64 keys
 constexpr int kSmem = 1024 + 4 * kTileBytes + kStages * kStageBytes + 2 * kZBytes + 512;
-enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bDqFull = 11, bSpEmpty = 12, bNum = 14 };
+enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bDqFull = 14, bSpEmpty = 12, bNum = 16 };
 }  // namespace dq2
 
 template <bool kFp16>
@@ -618,7 +618,8 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(bar(bZEmpty + w), 1);
       mbar_init(bar(bSpEmpty + w), 4);
     }
-    mbar_init(bar(bDqFull), issuers);
+    mbar_init(bar(bDqFull), 1);
+    mbar_init(bar(bDqFull + 1), 1);
     ctl->abort = 0;
     fence_barrier_init();
   }
@@ -691,12 +692,12 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mma_commit(bar(bZEmpty + w));
         mma_commit(bar(bKvEmpty + u % kStages));
       }
+      if (ok) mma_commit(bar(bDqFull + w));   // this tile's dQ is complete: its rows store it while the other tile goes on
       // tile a does not read the last sub-tiles: release them on its behalf once they have arrived
       for (int t = my_steps; ok && t < n_steps; ++t) {
         ok = wait_or_abort(bar(bKvFull + t % kStages), (t / kStages) & 1, abort_flag, p, 524);
         if (ok) mbar_arrive(bar(bKvEmpty + t % kStages));
       }
-      if (ok) mma_commit(bar(bDqFull));
     }
   } else {
     // ------------------------------------------------ rows: warpgroup w owns query tile Ia + w
@@ -751,7 +752,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(bZFull + w));
     }
-    if (ok && my_steps > 0) ok = wait_or_abort(bar(bDqFull), 0, abort_flag, p, 532);
+    if (ok && my_steps > 0) ok = wait_or_abort(bar(bDqFull + w), 0, abort_flag, p, 532);
     if (ok && my_steps > 0) {
       tc_fence_after();
       const uint32_t t_acc = tmem + 256 + w * 128 + lane_off;

@@ -25,7 +25,7 @@ constexpr int kStageBytes = 2 * kKvTileBytes; // K and V
 constexpr int kPBytes = kBM * kBN * 2;        // one P buffer: 128 rows x 64 keys
 constexpr int kBarBytes = 512;
 constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
-enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bQFree = 11, bOFree = 12, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 24 };
+enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bQFree = 11, bOFree = 12, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 25 };
 // per-warpgroup barrier index: base + wg * 2 + buf
 }  // namespace fwd256
 
@@ -158,7 +158,8 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(bar(bPFull + s), 4);
       mbar_init(bar(bPEmpty + s), 1);
     }
-    mbar_init(bar(bOFull), 2);
+    mbar_init(bar(bOFull), 1);
+    mbar_init(bar(bOFull + 1), 1);
     mbar_init(bar(bOFree), 4);
     mbar_init(bar(bOFree + 1), 4);
     ctl->abort = 0;
@@ -259,7 +260,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         if (!ok) break;
         if (!active) mma_commit(bar(bQFree));   // after this thread's earlier MMAs, like every arrival on these two
-        mma_commit(bar(bOFull));
+        mma_commit(bar(bOFull + wg));   // this tile's O is complete (an idle tile: behind its earlier MMAs)
         T += w.n_steps;
         U += my_steps;
       }
@@ -309,7 +310,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       // ---- epilogue: O (TMEM) -> global, rem, log_rem
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 42 + wg, it);
-      if (ok) ok = wait_or_abort(bar(bOFull), it & 1, abort_flag, p, 332);
+      if (ok) ok = wait_or_abort(bar(bOFull + wg), it & 1, abort_flag, p, 332);
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 44 + wg, it);
       if (ok && my_steps > 0) {
         tc_fence_after();
