@@ -165,6 +165,10 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   k.scale = p->logit_scale;
   k.check_leading_zero = (p->cu_seqlens != nullptr && (p->flags & SB_FLAG_CHECK_LEADING_ZERO)) ? 1 : 0;
   k.dbg = p->reserved & 0xff;
+  // Tiles of one sequence that stay neighbours in the launch order.  The backward kernels gain more from sharing
+  // K/V or Q/dO reads through L2 (measured: -4 % at 2048-token, -8 % at 4096-token sequences) than they lose in the
+  // tail; the forward's blocks are persistent with a fixed item assignment, which wants the pure weight order.
+  k.order_span = backward ? 16 : 1;
   k.trace_mode = (p->reserved >> 8) & 3;
   k.trace = (p->reserved & 0x100) ? reinterpret_cast<unsigned long long *>(ws_end - kTraceBytes) : nullptr;
   k.skip_dq = (p->flags & SB_FLAG_BWD_SKIP_DQ) ? 1 : 0;

@@ -40,6 +40,7 @@ struct KParams {
   int skip_dq, skip_dkv;   // timing aids: leave one of the two backward kernels out
   const int2 *order;       // packed batches: work items by descending weight, see decode_item
   const int2 *order2;      // the same for every second tile (backward only)
+  int order_span;          // entries of one sequence that stay neighbours in order / order2 (>= 1)
   int trace_mode;          // diagnostics builds: bit 1 = log every block's SM, start, first row work and end time
   int dbg;                 // experiments only (SbParams.reserved): 0 = normal arithmetic
   unsigned long long *trace;  // experiments only: event log of block (0,0) in the workspace tail, or nullptr

@@ -20,8 +20,10 @@ namespace sb {
 // ------------------------------------------------------------------------------------------------
 // Sequence table: exclusive prefix of tiles per sequence and of (query tile, key tile) pairs.
 // ------------------------------------------------------------------------------------------------
-// Work items by descending weight (see decode_item): a counting sort over the classes k / group, the heaviest
-// class first; inside a class the order is whatever the shared-memory atomics give, which does not matter.
+// Work items by descending weight (see decode_item): a counting sort over classes of `order_span` consecutive tiles
+// (counted in units of `group`), the heaviest class first.  The tiles of one sequence inside a class stay neighbours
+// (they read the same keys or queries at about the same time and share them through L2); the order of the
+// sequences inside a class is whatever the shared-memory atomics give, which does not matter.
 constexpr int kMaxClasses = 8192;
 __device__ __forceinline__ int seq_tiles(const KParams &p, int s) {
   const long long start = s == 0 ? 0 : load_cu(p, s - 1);
@@ -31,8 +33,10 @@ __device__ __forceinline__ int seq_tiles(const KParams &p, int s) {
 }
 __device__ void build_order(const KParams &p, int group, int2 *out, int hdr_slot, int *s_cls) {
   const int t = threadIdx.x;
-  const int m_max = (p.n_max + group - 1) / group;
-  if (m_max > kMaxClasses) {   // sequences beyond a million tokens: sequence by sequence, serially
+  const int span = p.order_span;                         // entries of one sequence that stay neighbours
+  const int m_max = (p.n_max + group - 1) / group;       // entries of the longest sequence
+  const int c_max = (m_max + span - 1) / span;           // classes
+  if (c_max > kMaxClasses) {   // sequences beyond millions of tokens: sequence by sequence, serially
     if (t == 0) {
       int pos = 0;
       for (int s = 0; s < p.num_seq; ++s)
@@ -42,26 +46,30 @@ __device__ void build_order(const KParams &p, int group, int2 *out, int hdr_slot
     __syncthreads();
     return;
   }
-  for (int j = t; j < m_max; j += blockDim.x) s_cls[j] = 0;
+  for (int j = t; j < c_max; j += blockDim.x) s_cls[j] = 0;
   __syncthreads();
-  for (int s = t; s < p.num_seq; s += blockDim.x) {
+  for (int s = t; s < p.num_seq; s += blockDim.x) {   // entries per class
     const int m = (seq_tiles(p, s) + group - 1) / group;
-    if (m > 0) atomicAdd(&s_cls[m - 1], 1);
+    for (int cl = 0; cl * span < m; ++cl) atomicAdd(&s_cls[cl], min(span, m - cl * span));
   }
   __syncthreads();
-  if (t == 0) {   // s_cls[j]: sequences whose last class is j  ->  first position of class j
-    int longer = 0, pos = 0;
-    for (int j = m_max - 1; j >= 0; --j) {
-      longer += s_cls[j];
-      s_cls[j] = pos;
-      pos += longer;
+  if (t == 0) {   // -> first position of every class, the heaviest class first
+    int pos = 0;
+    for (int cl = c_max - 1; cl >= 0; --cl) {
+      const int n = s_cls[cl];
+      s_cls[cl] = pos;
+      pos += n;
     }
     p.hdr[hdr_slot] = pos;
   }
   __syncthreads();
   for (int s = t; s < p.num_seq; s += blockDim.x) {
     const int m = (seq_tiles(p, s) + group - 1) / group;
-    for (int j = 0; j < m; ++j) out[atomicAdd(&s_cls[j], 1)] = make_int2(s, j * group);
+    for (int cl = 0; cl * span < m; ++cl) {
+      const int n = min(span, m - cl * span);
+      const int pos = atomicAdd(&s_cls[cl], n);
+      for (int i = 0; i < n; ++i) out[pos + i] = make_int2(s, (cl * span + n - 1 - i) * group);   // heaviest first
+    }
   }
   __syncthreads();
 }
