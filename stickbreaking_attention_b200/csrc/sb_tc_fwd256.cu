@@ -1,4 +1,4 @@
-// Tensor-core forward kernel for head sizes 72..128: 256 query rows per CTA.
+// Tensor-core forward kernel for bf16 / fp16 tensors: 256 query rows per work item, persistent blocks.
 //
 // Reference counterpart: _forward_one_row, sb_varlen_fwd.py:81-215.  A CTA owns two adjacent 128-row query tiles
 // (a: rows 0..127, b: rows 128..255 of its 256-row block) of one (sequence, head) and streams 64-key K/V
@@ -18,13 +18,17 @@ namespace fwd256 {
 constexpr int kThreads = 352;
 constexpr int kBN = 64;                       // keys per sub-tile
 constexpr int kStages = 3;
-constexpr int kQBytes = kBM * 128 * 2;        // one 128-row Q tile (two 128x64 boxes)
 constexpr int kKvBoxBytes = kBN * 64 * 2;     // one 64-row x 64-column box
-constexpr int kKvTileBytes = 2 * kKvBoxBytes; // K or V sub-tile: 64 keys x 128 columns
-constexpr int kStageBytes = 2 * kKvTileBytes; // K and V
 constexpr int kPBytes = kBM * kBN * 2;        // one P buffer: 128 rows x 64 keys
 constexpr int kBarBytes = 512;
-constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
+template <int D>                              // D: head size rounded up to 64 or 128
+struct Cfg {
+  static constexpr int kBoxes = D / 64;                        // 64-column blocks per row
+  static constexpr int kQBytes = kBM * D * 2;                  // one 128-row Q tile
+  static constexpr int kKvTileBytes = kBoxes * kKvBoxBytes;    // K or V sub-tile: 64 keys x D columns
+  static constexpr int kStageBytes = 2 * kKvTileBytes;         // K and V
+  static constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
+};
 enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bQFree = 11, bOFree = 12, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 25 };
 // per-warpgroup barrier index: base + wg * 2 + buf
 }  // namespace fwd256
@@ -124,12 +128,13 @@ __device__ __forceinline__ bool fwd256_item(const KParams &p, int it, Fwd256Item
 // below), so the loads and first MMAs of the next item overlap the last row pass and the epilogue of the current one.
 // Per item and role the barriers advance by fixed amounts whether or not tile b exists: an idle issuer still commits
 // and releases the K/V stages (after they were filled, so that it cannot run ahead of a phase).
-template <bool kFp16>
+template <int D, bool kFp16>
 __global__ void __launch_bounds__(fwd256::kThreads, 1)
 tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const KParams p) {
   using namespace fwd256;
-  constexpr int D = 128;
+  using C = Cfg<D>;
+  constexpr int kQBytes = C::kQBytes, kKvTileBytes = C::kKvTileBytes, kStageBytes = C::kStageBytes, kBoxes = C::kBoxes;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
@@ -186,7 +191,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int qrow = (int)w.c.tok0 + w.blk_row0;
         mbar_arrive_expect_tx(bar(bQ), 2 * kQBytes);
         for (int t = 0; t < 2; ++t)
-          for (int kb = 0; kb < 2; ++kb)
+          for (int kb = 0; kb < kBoxes; ++kb)
             tma_load_4d(sQ + t * kQBytes + kb * kBoxBytes, &tm_q, bar(bQ), kb * 64, qrow + t * kBM, w.h, (int)w.c.boff);
         bool ok = true;
         for (int t = 0; t < w.n_steps; ++t) {
@@ -197,7 +202,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint32_t dst = sKV + st * kStageBytes;
           trace_event(p, 0, tr_cur, 1, t);
           mbar_arrive_expect_tx(bar(bKvFull + st), kStageBytes);
-          for (int kb = 0; kb < 2; ++kb) {
+          for (int kb = 0; kb < kBoxes; ++kb) {
             tma_load_4d(dst + kb * kKvBoxBytes, &tm_k, bar(bKvFull + st), kb * 64, krow, w.h, (int)w.c.boff);
             tma_load_4d(dst + kKvTileBytes + kb * kKvBoxBytes, &tm_v, bar(bKvFull + st), kb * 64, krow, w.h, (int)w.c.boff);
           }
@@ -325,8 +330,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (lane == 0) {
             const uint32_t src = sP + wg * 2 * kPBytes + (warp & 3) * 32 * 128;
             const int trow = (int)w.c.tok0 + tile_row0 + (warp & 3) * 32;
-            tma_store_4d(&tm_o, src, 0, trow, w.h, (int)w.c.boff);
-            tma_store_4d(&tm_o, src + kPBytes, 64, trow, w.h, (int)w.c.boff);
+            for (int kb = 0; kb < kBoxes; ++kb) tma_store_4d(&tm_o, src + kb * kPBytes, kb * 64, trow, w.h, (int)w.c.boff);
             tma_store_commit();
           }
         } else {
@@ -355,7 +359,8 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
-cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s) {
+template <int D, bool kFp16>
+static cudaError_t launch_t(const KParams &p, int dtype, cudaStream_t s) {
   CUtensorMap mq, mk, mv, mo;
   cudaError_t e;
   if ((e = make_tile_map(&mq, p.q, p, dtype, kBM)) != cudaSuccess) return e;
@@ -366,16 +371,17 @@ cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s) {
   if ((e = sm_count(&sms)) != cudaSuccess) return e;
   const long long blocks = item_blocks(p, 1);
   const dim3 grid((unsigned)(blocks < sms ? blocks : sms));   // one resident block per SM
-  if (dtype == SB_DTYPE_F16) {
-    auto kernel = tc_fwd256_kernel<true>;
-    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
-    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, mo, p);
-  } else {
-    auto kernel = tc_fwd256_kernel<false>;
-    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd256::kSmem)) != cudaSuccess) return e;
-    kernel<<<grid, fwd256::kThreads, fwd256::kSmem, s>>>(mq, mk, mv, mo, p);
-  }
+  auto kernel = tc_fwd256_kernel<D, kFp16>;
+  constexpr int smem = fwd256::Cfg<D>::kSmem;
+  if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+  kernel<<<grid, fwd256::kThreads, smem, s>>>(mq, mk, mv, mo, p);
   return cudaGetLastError();
+}
+
+cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s) {
+  const bool f16 = dtype == SB_DTYPE_F16;
+  if (p.head_dim <= 64) return f16 ? launch_t<64, true>(p, dtype, s) : launch_t<64, false>(p, dtype, s);
+  return f16 ? launch_t<128, true>(p, dtype, s) : launch_t<128, false>(p, dtype, s);
 }
 
 }  // namespace sb
