@@ -201,7 +201,7 @@ static int run(const SbParams *p, void *stream, bool backward) {
   if (p->tokens == 0) return SB_OK;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e = launch_prep(k, s);
-  g_launches += (p->cu_seqlens != nullptr) ? 2 : 1;
+  g_launches += (p->cu_seqlens != nullptr && k.trace != nullptr) ? 2 : 1;   // prep kernel or header clear (both with the event log)
   if (e != cudaSuccess) return fail(SB_ERR_CUDA, "prep launch: %s", cudaGetErrorString(e));
   const int chunk = backward ? pl.chunk_heads : p->heads;
   for (int h0 = 0; h0 < p->heads; h0 += chunk) {

@@ -79,8 +79,11 @@ __global__ void __launch_bounds__(256) prep_kernel(KParams p) {
   __shared__ long long s_tiles[256];
   __shared__ long long s_pairs[256];
   const int t = threadIdx.x;
+  if (t < 8) p.hdr[t] = 0;   // the header is this kernel's to initialise (a fixed-length batch uses clear_hdr_kernel)
+  __syncthreads();
   const int per = (p.num_seq + 255) / 256;
   const int s0 = t * per, s1 = min(p.num_seq, s0 + per);
+  const int busy = (p.num_seq + per - 1) / per;   // threads that own sequences
   long long tiles = 0, pairs = 0;
   int bad = -1;
   for (int s = s0; s < s1; ++s) {
@@ -105,7 +108,7 @@ __global__ void __launch_bounds__(256) prep_kernel(KParams p) {
       if (p.status != nullptr) { p.status[0] = SB_DEV_BAD_CU_SEQLENS; p.status[1] = -1; }
     }
     long long a = 0, b = 0;
-    for (int i = 0; i < 256; ++i) {
+    for (int i = 0; i < busy; ++i) {
       const long long x = s_tiles[i], y = s_pairs[i];
       s_tiles[i] = a; s_pairs[i] = b;
       a += x; b += y;
@@ -141,7 +144,7 @@ __global__ void clear_hdr_kernel(int *hdr, unsigned long long *trace) {
 }
 
 cudaError_t launch_prep(const KParams &p, cudaStream_t s) {
-  clear_hdr_kernel<<<1, 32, 0, s>>>(p.hdr, p.trace);
+  if (p.cu == nullptr || p.trace != nullptr) clear_hdr_kernel<<<1, 32, 0, s>>>(p.hdr, p.trace);
   if (p.cu != nullptr) prep_kernel<<<1, 256, 0, s>>>(p);
   return cudaGetLastError();
 }
