@@ -1035,7 +1035,8 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       int round = 0;
 #pragma unroll 1
       for (int hf = 0; hf < n_halves && ok; ++hf) {
-        const bool full = J * kBM + hf * kBN + kBN <= c.len && p.head_dim == D;   // the same for all row warps
+        // the same for all row warps; columns at and beyond head_dim lie outside the tensor map and are not written
+        const bool full = J * kBM + hf * kBN + kBN <= c.len;
 #pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t va[16];

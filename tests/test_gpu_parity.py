@@ -78,7 +78,7 @@ RAGGED = [1, 2, 63, 64, 65, 127, 128, 129, 31, 300]
 
 @pytest.mark.parametrize("ac", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("d", [64, 72, 96, 128])
 def test_varlen_ragged(sb, cuda_device, dtype, d, ac):
     ins = H.make_inputs((3, sum(RAGGED), d), dtype, seed=d + int(ac))
     cu = cu_of(RAGGED)
@@ -89,7 +89,7 @@ def test_varlen_ragged(sb, cuda_device, dtype, d, ac):
         assert torch.all(got[0][:, starts] == 0) and torch.all(got[1][:, starts] == 1)
 
 
-@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("d", [64, 104, 128])
 def test_varlen_many_uneven_sequences(sb, cuda_device, d):
     """More work items than SMs, lengths from 1 token to 21 tiles: exercises the weight-ordered item tables
     (several classes, sequences longer than one class span) and the persistent forward's walk over them."""
