@@ -63,8 +63,14 @@ enum SbFlags {
                             status[1] = -1.  Replaces the reference's host-side assert, which
                             forces a device synchronisation.                                    */
   SB_FLAG_BWD_SKIP_DKV = 4, /* timing aid: sb_bwd enqueues only the dQ kernel                   */
-  SB_FLAG_BWD_SKIP_DQ = 8   /* timing aid: sb_bwd enqueues only the dK/dV kernel, which then reads
-                            the boundary values a previous full sb_bwd left in the same workspace */
+  SB_FLAG_BWD_SKIP_DQ = 8,  /* timing aid: sb_bwd enqueues only the dK/dV kernel, which then reads
+                            what a previous full sb_bwd left in the same workspace              */
+  SB_FLAG_BWD_RECOMPUTE = 16 /* small-workspace backward.  By default (16-bit tensors, head_dim 72..128)
+                            the dQ kernel stores its A and dz tiles -- 64 KiB per (query tile, key tile)
+                            pair and head, heads processed in chunks of at most 8 GiB -- and the dK/dV
+                            kernel is two plain GEMMs over them.  With this flag, or when one head
+                            exceeds 8 GiB, the dK/dV kernel recomputes the tiles from boundary values
+                            (a few KiB per pair).  Same 16-bit tiles either way.                 */
 };
 
 typedef struct SbTensor {

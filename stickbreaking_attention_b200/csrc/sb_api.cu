@@ -23,7 +23,9 @@ static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; 
 
 // Workspace layout, a pure function of the shapes:
 //   [hdr 256 B][tile_prefix int32 x (num_seq+1)][pair_prefix int64 x (num_seq+1)]
-//   backward only: [R1 fp32 x chunk_heads x pairs_cap x halves x tile][S2 same]
+//   packed batches: [order int2 x tiles][order2 (backward) int2 x tiles]
+//   backward, either: [A | dz tiles, 16-bit x chunk_heads x pairs_cap x 2 x 128 x 128]   (stored-tiles mode)
+//             or:     [R1 fp32 x chunk_heads x pairs_cap x halves x tile][S2 same]       (recompute mode)
 struct Plan {
   int path;
   int tile;
@@ -35,6 +37,8 @@ struct Plan {
   int bnd_halves;             // boundary records per (query tile, key tile) pair
   size_t bnd_bytes_per_head;  // one of the two arrays
   int chunk_heads;
+  bool store_az;              // backward: the dq kernel stores its A and dz tiles for the dK/dV kernel
+  size_t az_bytes_per_head;
   size_t total_fwd, total_bwd;
 };
 
@@ -99,13 +103,19 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   // the tensor-core path records the carried values four times per 128-key tile
   pl.bnd_halves = tc ? 4 : 1;   // keys 0, 32, 64, 96 of every 128-key tile
   pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * pl.bnd_halves * sizeof(float), 256);
-  size_t chunk = pl.bnd_bytes_per_head ? kBoundaryBudget / (2 * pl.bnd_bytes_per_head) : (size_t)p->heads;
+  // Stored-tiles mode (128-column head sizes): 64 KiB per (query tile, key tile) pair and head.  Taken when at least one
+  // head fits the budget and the caller did not ask for the small-workspace mode.
+  pl.az_bytes_per_head = (size_t)pl.pairs_cap * 2 * kTcTile * kTcTile * 2;
+  pl.store_az = backward && tc && p->head_dim > 64 && !(p->flags & SB_FLAG_BWD_RECOMPUTE) &&
+                pl.az_bytes_per_head <= kBoundaryBudget;
+  const size_t per_head = pl.store_az ? pl.az_bytes_per_head : 2 * pl.bnd_bytes_per_head;
+  size_t chunk = per_head ? kBoundaryBudget / per_head : (size_t)p->heads;
   if (chunk < 1) chunk = 1;
   if (chunk > (size_t)p->heads) chunk = p->heads;
   pl.chunk_heads = (int)chunk;
   const size_t trace_bytes = (p->reserved & 0x100) ? kTraceBytes : 0;   // experiments only
   pl.total_fwd = pl.off_bnd + trace_bytes;
-  pl.total_bwd = pl.off_bnd + 2 * pl.bnd_bytes_per_head * chunk + trace_bytes;
+  pl.total_bwd = pl.off_bnd + per_head * chunk + trace_bytes;
   return SB_OK;
 }
 
@@ -182,9 +192,13 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
     k.order = reinterpret_cast<const int2 *>(ws + pl.off_order);
     if (pl.off_bnd != pl.off_order2) k.order2 = reinterpret_cast<const int2 *>(ws + pl.off_order2);
   }
-  k.bnd_r1 = reinterpret_cast<float *>(ws + pl.off_bnd);
-  k.bnd_s2 = reinterpret_cast<float *>(ws + pl.off_bnd + pl.bnd_bytes_per_head * pl.chunk_heads);
-  k.pairs_cap = (long long)(pl.bnd_bytes_per_head / ((size_t)pl.tile * pl.bnd_halves * sizeof(float)));
+  if (backward && pl.store_az) {
+    k.az = reinterpret_cast<unsigned short *>(ws + pl.off_bnd);
+  } else {
+    k.bnd_r1 = reinterpret_cast<float *>(ws + pl.off_bnd);
+    k.bnd_s2 = reinterpret_cast<float *>(ws + pl.off_bnd + pl.bnd_bytes_per_head * pl.chunk_heads);
+  }
+  k.pairs_cap = pl.pairs_cap;
   k.status = p->status;
   return SB_OK;
 }

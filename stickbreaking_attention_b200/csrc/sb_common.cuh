@@ -50,6 +50,7 @@ struct KParams {
   long long *pair_prefix;  // [num_seq + 1] exclusive prefix of n(n+1)/2 (varlen)
   float *bnd_r1;       // [head_cnt][pairs_cap][tile]  suffix sums of log(1-beta) at tile starts
   float *bnd_s2;       // [head_cnt][pairs_cap][tile]  prefix sums of G before each key tile
+  unsigned short *az;  // stored-tiles mode: [head_cnt][pairs_cap][A, dz][128 query rows][128 keys], 16-bit; else null
   long long pairs_cap;
   int *status;
 };

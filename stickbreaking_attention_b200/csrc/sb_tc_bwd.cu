@@ -506,13 +506,16 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 // One row of a 64-key strip: four 16-column chunks, TMEM read one chunk ahead.  mc0: key index of the strip's first
 // column inside its 128-key tile (for the diagonal mask).  empty_bar (optional) is signalled, one arrival per warp,
 // once the last S/dP columns are in registers; gate_bar (optional) is waited for before the first store to the
-// output tiles, i.e. after the first chunk's arithmetic.  Returns false if that wait gave up.
+// output tiles, i.e. after the first chunk's arithmetic.  az_a / az_z (optional): this row's 64 values of the stored
+// A and dz tiles in global memory (plain row-major, 16-bit), written next to the shared-memory dz tile.
+// Returns false if the gate wait gave up.
 template <bool kFp16, bool kStoreA, bool kMasked>
 __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
                                               float scale2, float r1, float gpre, float dr, float &gs, float &logsum,
                                               uint8_t *tile_a, uint8_t *tile_z, float *mid_r1 = nullptr,
                                               float *mid_s2 = nullptr, uint32_t empty_bar = 0, uint32_t gate_bar = 0,
-                                              uint32_t gate_parity = 0) {
+                                              uint32_t gate_parity = 0, unsigned short *az_a = nullptr,
+                                              unsigned short *az_z = nullptr) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
   bool ok = true;
   tmem_ld16(ts, s0);
@@ -531,7 +534,15 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
         tc_fence_after();
       }
       if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
-      store_row_chunk16<kFp16>(tile_z, r, c0, pz);
+      uint32_t wz[8];
+      pack_row_chunk16<kFp16>(pz, wz);
+      store_packed_chunk16(tile_z, r, c0, wz);
+      if (az_a != nullptr) {
+        uint32_t wa[8];
+        pack_row_chunk16<kFp16>(pa, wa);
+        store_packed_global16(az_a + c0, wa);
+        store_packed_global16(az_z + c0, wz);
+      }
     }
     tmem_wait_ld_regs(s1, d1);
     if (pair == 0) {
@@ -542,8 +553,20 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
       __syncwarp();
       if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
     }
-    bwd_row_chunk<kFp16, kStoreA, kMasked>(s1, d1, c0 + 16, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs,
-                                        logsum, tile_a, tile_z);
+    {
+      float pa[16], pz[16];
+      bwd_row_chunk_values<kMasked>(s1, d1, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
+      if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0 + 16, pa);
+      uint32_t wz[8];
+      pack_row_chunk16<kFp16>(pz, wz);
+      store_packed_chunk16(tile_z, r, c0 + 16, wz);
+      if (az_a != nullptr) {
+        uint32_t wa[8];
+        pack_row_chunk16<kFp16>(pa, wa);
+        store_packed_global16(az_a + c0 + 16, wa);
+        store_packed_global16(az_z + c0 + 16, wz);
+      }
+    }
     if (pair == 0 && mid_r1 != nullptr) {   // the carried values after 32 of the 64 columns
       *mid_r1 = r1 + logsum;
       *mid_s2 = gpre + gs;
@@ -718,6 +741,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
     // boundary records: [pair (I, J)][half][row]; sub-tile u is half u & 1 of key tile u >> 1
     const long long rec0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (4 * kBM) + r;
+    const bool ragged = I * kBM + kBM > c.len;   // the sequence ends inside this tile
     bool ok = true;
     for (int u = 0; u < my_steps && ok; ++u) {
       ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 530);
@@ -727,19 +751,36 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // the dz tile is still being read by the previous step's dQ MMAs: waited for inside the pass, before its first store
       const uint32_t gate = u >= 1 ? bar(bZEmpty + w) : 0u, gate_parity = (u - 1) & 1;
       const float r1f = (float)r1;
-      float *rec_r1 = p.bnd_r1 + rec0 + (long long)u * (2 * kBM);   // quarter 2 (u & 1) of key tile u >> 1
-      float *rec_s2 = p.bnd_s2 + rec0 + (long long)u * (2 * kBM);
-      rec_r1[0] = r1f;
-      rec_s2[0] = gpre;
       float gs = 0.f, logsum = 0.f;
       bool pass_ok;
-      if (u >= 2 * I)
-        pass_ok = strip_row_pass<kFp16, false, true>(tS, tP, r, (u - 2 * I) * kBN, true, p.attend_current, true, scale2, r1f, gpre,
-                                                     dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w),
-                                                     gate, gate_parity);
-      else
-        pass_ok = strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
-                                                      rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w), gate, gate_parity);
+      // a tile with rows past the sequence end takes the masking variant throughout: those rows must be zero in the
+      // stored tiles (the dK/dV GEMMs sum over all 128 query rows)
+      const bool on_diag = u >= 2 * I;
+      if (p.az != nullptr) {
+        // stored-tiles mode: this row's 64 values of A and dz for key tile u >> 1, half u & 1
+        const long long pair = c.pair0 + (long long)I * (I + 1) / 2 + (u >> 1);
+        unsigned short *az_a = p.az + ((((long long)hh * 2) * p.pairs_cap + pair) * kBM + r) * kBM + (u & 1) * kBN;
+        unsigned short *az_z = az_a + p.pairs_cap * (long long)(kBM * kBM);
+        if (on_diag || ragged)
+          pass_ok = strip_row_pass<kFp16, false, true>(tS, tP, r, on_diag ? (u - 2 * I) * kBN : 0, on_diag, p.attend_current, valid,
+                                                       scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, nullptr, nullptr,
+                                                       bar(bSpEmpty + w), gate, gate_parity, az_a, az_z);
+        else
+          pass_ok = strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
+                                                        nullptr, nullptr, bar(bSpEmpty + w), gate, gate_parity, az_a, az_z);
+      } else {
+        float *rec_r1 = p.bnd_r1 + rec0 + (long long)u * (2 * kBM);   // quarter 2 (u & 1) of key tile u >> 1
+        float *rec_s2 = p.bnd_s2 + rec0 + (long long)u * (2 * kBM);
+        rec_r1[0] = r1f;
+        rec_s2[0] = gpre;
+        if (on_diag)
+          pass_ok = strip_row_pass<kFp16, false, true>(tS, tP, r, (u - 2 * I) * kBN, true, p.attend_current, true, scale2, r1f, gpre,
+                                                       dr, gs, logsum, nullptr, gZ, rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w),
+                                                       gate, gate_parity);
+        else
+          pass_ok = strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
+                                                        rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w), gate, gate_parity);
+      }
       if (!pass_ok) {   // the bounded wait inside the pass gave up
         *abort_flag = 1;
         if (p.status != nullptr) { p.status[0] = SB_DEV_WAIT_TIMEOUT; p.status[1] = 531; }
@@ -1086,6 +1127,154 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
+// =======================================================================================================
+// dK/dV from stored tiles (head sizes 72..128): two GEMMs per 128-key tile, no row passes
+// =======================================================================================================
+// In stored-tiles mode the dq kernel leaves the 16-bit A and dz tiles of every (query tile, key tile) pair in the
+// workspace.  This kernel owns one 128-key tile and walks its query tiles diagonal -> end, 64 query rows per stage:
+//   dK[keys x d] += dz^T Q,   dV[keys x d] += A^T dO      (M = 128 keys, N = 128 columns, K = 64 query rows)
+// with all four operands read row-major as "MN-major" tiles (rows = query rows = the contraction).  Accumulators sit
+// in TMEM with lanes = keys, so the epilogue writes plain rows.  Fixed summation order, no atomics.
+//   warp 4    TMA producer: per stage A, dz (from the workspace), Q, dO -- 64 KiB, three stages
+//   warp 5    MMA issuer
+//   warps 0-3 epilogue: dK, dV rows -> shared memory -> TMA stores
+// The kernel is bound by reading the stored tiles (64 KiB per 128x128 pair) from HBM.
+namespace dkv5 {
+constexpr int kThreads = 192;
+constexpr int kStages = 3;
+constexpr int kBox = 64 * 64 * 2;            // 64 rows x 64 columns, 16-bit
+constexpr int kStageBytes = 8 * kBox;        // A, dz, Q, dO: two 64-column blocks each
+constexpr int kSmem = 1024 + kStages * kStageBytes + 512;
+constexpr uint32_t kCols = 256;              // dK 0..127, dV 128..255
+enum { bFull = 0, bEmpty = 3, bOut = 6, bNum = 7 };
+}  // namespace dkv5
+
+template <bool kFp16>
+__global__ void __launch_bounds__(dkv5::kThreads, 1)
+tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_constant__ CUtensorMap tm_q,
+                   const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_dk,
+                   const __grid_constant__ CUtensorMap tm_dv, const KParams p) {
+  using namespace dkv5;
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  if (p.hdr[0]) return;
+  TileCoord c;
+  int hh;
+  if (!decode_block(p, 1, false, c, hh)) return;
+  const int h = p.head0 + hh;
+  const int J = c.idx;                        // the 128-key tile
+  const int n_stages = 2 * (c.n_tiles - J);   // stage t: query tile J + (t >> 1), rows (t & 1) * 64 .. + 64
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  const uint32_t sBar = base + kStages * kStageBytes;
+  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + bNum * 8);
+  volatile int *abort_flag = &ctl->abort;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar(bFull + s), 1); mbar_init(bar(bEmpty + s), 1); }
+    mbar_init(bar(bOut), 1);
+    ctl->abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      prefetch_tensormap(&tm_az); prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_g);
+      for (int t = 0; t < n_stages; ++t) {
+        const int st = t % kStages;
+        if (t >= kStages && !wait_or_abort(bar(bEmpty + st), ((t / kStages) - 1) & 1, abort_flag, p, 640)) break;
+        if (*abort_flag) break;
+        const int I = J + (t >> 1), hq = t & 1;
+        const long long pair = c.pair0 + (long long)I * (I + 1) / 2 + J;
+        const int az_row = (int)(pair * kBM) + hq * 64;
+        const int qrow = (int)c.tok0 + I * kBM + hq * 64;
+        const uint32_t dst = base + st * kStageBytes;
+        mbar_arrive_expect_tx(bar(bFull + st), kStageBytes);
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(dst + (0 + kb) * kBox, &tm_az, bar(bFull + st), kb * 64, az_row, 0, hh);   // A
+          tma_load_4d(dst + (2 + kb) * kBox, &tm_az, bar(bFull + st), kb * 64, az_row, 1, hh);   // dz
+          tma_load_4d(dst + (4 + kb) * kBox, &tm_q, bar(bFull + st), kb * 64, qrow, h, (int)c.boff);
+          tma_load_4d(dst + (6 + kb) * kBox, &tm_g, bar(bFull + st), kb * 64, qrow, h, (int)c.boff);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // all operands MN-major: rows = query rows (the contraction), two 64-column blocks kBox apart
+      constexpr uint32_t idesc = idesc_f16(kBM, D, kFp16, true, true);
+      bool ok = true;
+      for (int t = 0; ok && t < n_stages; ++t) {
+        const int st = t % kStages;
+        ok = wait_or_abort(bar(bFull + st), (t / kStages) & 1, abort_flag, p, 641);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a = base + st * kStageBytes;
+        const uint64_t dA = smem_desc_sw128(a, kBox, 1024), dZ = smem_desc_sw128(a + 2 * kBox, kBox, 1024);
+        const uint64_t dQ = smem_desc_sw128(a + 4 * kBox, kBox, 1024), dG = smem_desc_sw128(a + 6 * kBox, kBox, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)   // 16 query rows = 2048 bytes per step
+          mma_f16_ss(tmem, dZ + (uint64_t)(ks * 128), dQ + (uint64_t)(ks * 128), idesc, t > 0 || ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_f16_ss(tmem + 128, dA + (uint64_t)(ks * 128), dG + (uint64_t)(ks * 128), idesc, t > 0 || ks > 0);
+        mma_commit(bar(bEmpty + st));
+      }
+      if (ok) mma_commit(bar(bOut));
+    }
+  } else {
+    // ------------------------------------------------ epilogue: one thread per key row
+    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
+    const int r = threadIdx.x;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    if (wait_or_abort(bar(bOut), 0, abort_flag, p, 642)) {
+      tc_fence_after();
+      const int key = J * kBM + r;
+      const bool valid = key < c.len;
+      if (J * kBM + kBM <= c.len) {
+        // full tile: through the first two stages' memory (all MMAs are done), one TMA store per warp and half
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          uint8_t *stage = gbase + which * kStageBytes;                // [128 x 128] as two blocks of 128-byte rows
+          stage_acc_rows<D, kFp16>(tmem + which * 128 + lane_off, stage, r, which == 0 ? p.scale : 1.f);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t src = base + which * kStageBytes + warp * 32 * 128;
+            const int trow = (int)c.tok0 + J * kBM + warp * 32;
+            const CUtensorMap *omap = which == 0 ? &tm_dk : &tm_dv;
+            tma_store_4d(omap, src, 0, trow, h, (int)c.boff);
+            tma_store_4d(omap, src + kBoxBytes, 64, trow, h, (int)c.boff);
+            tma_store_commit();
+          }
+        }
+        if (lane == 0) tma_store_wait_all();
+      } else {
+        // the sequence ends inside the tile: row by row, rows past the end are left alone
+        T *krow = reinterpret_cast<T *>(p.dk.ptr) + c.boff * p.dk.sb + (long long)h * p.dk.sh + (c.tok0 + key) * p.dk.st;
+        T *vrow = reinterpret_cast<T *>(p.dv.ptr) + c.boff * p.dv.sb + (long long)h * p.dv.sh + (c.tok0 + key) * p.dv.st;
+        store_acc_rows<D, kFp16, T>(tmem + lane_off, krow, valid, p.head_dim, p.scale);
+        store_acc_rows<D, kFp16, T>(tmem + 128 + lane_off, vrow, valid, p.head_dim, 1.f);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, kCols);
+}
+
 // -------------------------------------------------------------------------------------------------------
 template <int D, bool kFp16>
 static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
@@ -1116,7 +1305,19 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     kernel<<<grid, kTcThreads, DqCfg<D>::kSmem, s>>>(mq, mk, mv, mg, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
-  if (!p.skip_dkv && D == 128) {
+  if (!p.skip_dkv && D == 128 && p.az != nullptr) {
+    auto kernel = tc_bwd_dkv5_kernel<kFp16>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv5::kSmem);
+    if (e != cudaSuccess) return e;
+    CUtensorMap maz, mq64, mg64, mdk, mdv;
+    if ((e = make_az_map(&maz, p, dtype)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mq64, p.q, p, dtype, 64)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mg64, p.d_o, p, dtype, 64)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mdk, p.dk, p, dtype, 32)) != cudaSuccess) return e;   // stores: 32 rows per warp
+    if ((e = make_tile_map(&mdv, p.dv, p, dtype, 32)) != cudaSuccess) return e;
+    kernel<<<grid, dkv5::kThreads, dkv5::kSmem, s>>>(maz, mq64, mg64, mdk, mdv, p);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  } else if (!p.skip_dkv && D == 128) {
     auto kernel = tc_bwd_dkv4_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv4::kSmem);
     if (e != cudaSuccess) return e;

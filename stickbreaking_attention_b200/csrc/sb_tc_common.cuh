@@ -77,6 +77,23 @@ __device__ __forceinline__ void store_row_chunk16(uint8_t *tile, int r, int c0, 
   }
 }
 
+// The same in two steps: 16 values packed into eight 32-bit registers, which can go to several places.
+template <bool kFp16>
+__device__ __forceinline__ void pack_row_chunk16(const float (&x)[16], uint32_t (&w)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = pack2<kFp16>(x[2 * i], x[2 * i + 1]);
+}
+__device__ __forceinline__ void store_packed_chunk16(uint8_t *tile, int r, int c0, const uint32_t (&w)[8]) {
+  *reinterpret_cast<uint4 *>(tile + sw128_chunk_offset(r, c0)) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4 *>(tile + sw128_chunk_offset(r, c0 + 8)) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+// 16 consecutive 16-bit values of a plain row-major global row (32 bytes, 32-byte aligned)
+__device__ __forceinline__ void store_packed_global16(unsigned short *dst, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]),
+               "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");   // one full 32-byte sector per thread
+}
+
 // TMEM accumulator rows (one per thread) -> 16-bit global rows, `mul` applied, columns >= head_dim dropped.
 template <int D, bool kFp16, typename T>
 __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool valid, int head_dim, float mul) {
@@ -153,5 +170,7 @@ __device__ __forceinline__ void mma_mnmajor_mnmajor(uint32_t d_tmem, uint32_t a_
 
 // host: 4-D TMA map (head_dim, tokens, heads, batch), [64 x 128 x 1 x 1] box, 128-byte swizzle, zero fill
 cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows = kBM);
+// host: 4-D TMA map of the stored A / dz tiles, (keys 128, pairs * 128 query rows, {A, dz}, heads), [64 x 64 x 1 x 1] box
+cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype);
 
 }  // namespace sb
