@@ -36,13 +36,13 @@ cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype) {
+cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype, int box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return cudaErrorNotSupported;
   const cuuint64_t tile_bytes = (cuuint64_t)kBM * kBM * 2;
   cuuint64_t dims[4] = {(cuuint64_t)kBM, (cuuint64_t)p.pairs_cap * kBM, 2, (cuuint64_t)p.head_cnt};
   cuuint64_t strides[3] = {(cuuint64_t)kBM * 2, (cuuint64_t)p.pairs_cap * tile_bytes, 2 * (cuuint64_t)p.pairs_cap * tile_bytes};
-  cuuint32_t box[4] = {64, 64, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, dtype == SB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, p.az,
                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

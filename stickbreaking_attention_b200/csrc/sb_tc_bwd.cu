@@ -507,7 +507,8 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 // column inside its 128-key tile (for the diagonal mask).  empty_bar (optional) is signalled, one arrival per warp,
 // once the last S/dP columns are in registers; gate_bar (optional) is waited for before the first store to the
 // output tiles, i.e. after the first chunk's arithmetic.  az_a / az_z (optional): this row's 64 values of the stored
-// A and dz tiles in global memory (plain row-major, 16-bit), written next to the shared-memory dz tile.
+// A and dz tiles in global memory (plain row-major, 16-bit), written next to the shared-memory dz tile (the caller may
+// instead copy the finished dz tile out of shared memory).
 // Returns false if the gate wait gave up.
 template <bool kFp16, bool kStoreA, bool kMasked>
 __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, int mc0, bool diag, int ac, bool row_valid,
@@ -541,7 +542,7 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
         uint32_t wa[8];
         pack_row_chunk16<kFp16>(pa, wa);
         store_packed_global16(az_a + c0, wa);
-        store_packed_global16(az_z + c0, wz);
+        if (az_z != nullptr) store_packed_global16(az_z + c0, wz);
       }
     }
     tmem_wait_ld_regs(s1, d1);
@@ -564,7 +565,7 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
         uint32_t wa[8];
         pack_row_chunk16<kFp16>(pa, wa);
         store_packed_global16(az_a + c0 + 16, wa);
-        store_packed_global16(az_z + c0 + 16, wz);
+        if (az_z != nullptr) store_packed_global16(az_z + c0 + 16, wz);
       }
     }
     if (pair == 0 && mid_r1 != nullptr) {   // the carried values after 32 of the 64 columns
@@ -601,7 +602,7 @@ template <bool kFp16>
 __global__ void __launch_bounds__(dq2::kThreads, 1)
 tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
-                  const __grid_constant__ CUtensorMap tm_dq, const KParams p) {
+                  const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_az, const KParams p) {
   using namespace dq2;
   constexpr int D = 128;
   extern __shared__ uint8_t smem_raw[];
@@ -760,7 +761,10 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // stored-tiles mode: this row's 64 values of A and dz for key tile u >> 1, half u & 1
         const long long pair = c.pair0 + (long long)I * (I + 1) / 2 + (u >> 1);
         unsigned short *az_a = p.az + ((((long long)hh * 2) * p.pairs_cap + pair) * kBM + r) * kBM + (u & 1) * kBN;
-        unsigned short *az_z = az_a + p.pairs_cap * (long long)(kBM * kBM);
+        unsigned short *az_z = nullptr;   // the dz tile leaves by TMA below
+        // this warp's copy of the previous step's dz rows has left shared memory before they are rewritten
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
         if (on_diag || ragged)
           pass_ok = strip_row_pass<kFp16, false, true>(tS, tP, r, on_diag ? (u - 2 * I) * kBN : 0, on_diag, p.attend_current, valid,
                                                        scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, nullptr, nullptr,
@@ -791,8 +795,17 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_before();          // this step's TMEM reads are done before the slots are handed back
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(bZFull + w));
+      if (lane == 0) {
+        mbar_arrive(bar(bZFull + w));
+        if (p.az != nullptr) {   // stored-tiles mode: this warp's 32 rows x 64 keys of dz, out of the shared-memory tile
+          const long long pair = c.pair0 + (long long)I * (I + 1) / 2 + (u >> 1);
+          tma_store_4d(&tm_az, sZ + w * kZBytes + (warp & 3) * 32 * 128, (u & 1) * kBN, (int)(pair * kBM) + (warp & 3) * 32, 1, hh);
+          tma_store_commit();
+        }
+      }
     }
+    if (lane == 0) tma_store_wait_read();   // the dz buffer is reused by the epilogue
+    __syncwarp();
     if (ok && my_steps > 0) ok = wait_or_abort(bar(bDqFull + w), 0, abort_flag, p, 532);
     if (ok && my_steps > 0) {
       tc_fence_after();
@@ -1294,9 +1307,11 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     auto kernel = tc_bwd_dq2_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq2::kSmem);
     if (e != cudaSuccess) return e;
-    CUtensorMap mdq;   // stores: 32 rows per warp
+    CUtensorMap mdq, maz32;   // stores: 32 rows per warp
     if ((e = make_tile_map(&mdq, p.dq, p, dtype, 32)) != cudaSuccess) return e;
-    kernel<<<grid_pairs, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, mdq, p);
+    if (p.az != nullptr) { if ((e = make_az_map(&maz32, p, dtype, 32)) != cudaSuccess) return e; }
+    else maz32 = mdq;         // not used
+    kernel<<<grid_pairs, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, mdq, maz32, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dq) {
     auto kernel = tc_bwd_dq_kernel<D, kFp16>;

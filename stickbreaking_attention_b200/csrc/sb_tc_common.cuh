@@ -171,6 +171,6 @@ __device__ __forceinline__ void mma_mnmajor_mnmajor(uint32_t d_tmem, uint32_t a_
 // host: 4-D TMA map (head_dim, tokens, heads, batch), [64 x 128 x 1 x 1] box, 128-byte swizzle, zero fill
 cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows = kBM);
 // host: 4-D TMA map of the stored A / dz tiles, (keys 128, pairs * 128 query rows, {A, dz}, heads), [64 x 64 x 1 x 1] box
-cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype);
+cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype, int box_rows = 64);
 
 }  // namespace sb
