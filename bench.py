@@ -432,10 +432,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small-workspace", action="store_true",
+                    help="backward recomputes the attention tiles in the dK/dV kernel instead of storing them")
     args = ap.parse_args()
     w = workload(args.workload)
     if args.impl == "reference":
         run_reference_arm(args, w)
+    elif args.small_workspace:
+        import stickbreaking_attention_b200 as sb
+        with sb.small_backward_workspace():
+            run_gpu_arm(args, w)
     else:
         run_gpu_arm(args, w)
 

@@ -26,7 +26,7 @@ from . import _cabi
 
 NAMESPACE = "stickbreaking_attention_b200"
 
-_state = {"force_simt": False, "launches": 0}
+_state = {"force_simt": False, "bwd_recompute": False, "launches": 0}
 _status_words: dict[int, torch.Tensor] = {}
 
 
@@ -39,6 +39,19 @@ def force_simt(enabled: bool = True):
         yield
     finally:
         _state["force_simt"] = old
+
+
+@contextlib.contextmanager
+def small_backward_workspace(enabled: bool = True):
+    """Within the block the backward keeps its workspace small: the dK/dV kernel recomputes the attention tiles from
+    boundary values (a few KiB per tile pair) instead of reading the 64 KiB per pair the dQ kernel would store for it
+    (``SB_FLAG_BWD_RECOMPUTE``).  Slower at head sizes 72..128, same results to rounding."""
+    old = _state["bwd_recompute"]
+    _state["bwd_recompute"] = enabled
+    try:
+        yield
+    finally:
+        _state["bwd_recompute"] = old
 
 
 def kernel_launches() -> int:
@@ -107,6 +120,7 @@ def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_c
     prm.attend_current = int(bool(attend_current))
     prm.logit_scale = float(logit_scale)
     prm.flags = (_cabi.SB_FLAG_FORCE_SIMT if _state["force_simt"] else 0) | \
+                (_cabi.SB_FLAG_BWD_RECOMPUTE if _state["bwd_recompute"] else 0) | \
                 (_cabi.SB_FLAG_CHECK_LEADING_ZERO if leading_zero else 0)
     prm.q = _cabi.tensor_arg(q, fixed)
     prm.k = _cabi.tensor_arg(k, fixed)

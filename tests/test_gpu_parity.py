@@ -103,6 +103,22 @@ def test_varlen_many_uneven_sequences(sb, cuda_device, d):
     H.assert_parity(got, H.oracle_varlen(*ins, cu), torch.bfloat16, "uneven")
 
 
+def test_backward_modes_agree(sb, cuda_device):
+    """Default backward (the dQ kernel stores its A / dz tiles, dK/dV are GEMMs over them) against the small-workspace
+    backward (dK/dV recomputed from boundary values): both within the bound of the oracle and close to each other."""
+    lengths = [700, 129, 1, 1333, 64, 512]
+    ins = H.make_inputs((3, sum(lengths), 128), torch.bfloat16, seed=11)
+    cu = cu_of(lengths)
+    want = H.oracle_varlen(*ins, cu)
+    stored = H.run_varlen(sb, *ins, cu, cuda_device, max_seqlens=max(lengths))
+    with sb.small_backward_workspace():
+        recomputed = H.run_varlen(sb, *ins, cu, cuda_device, max_seqlens=max(lengths))
+    H.assert_parity(stored, want, torch.bfloat16, "stored tiles")
+    H.assert_parity(recomputed, want, torch.bfloat16, "recomputed tiles")
+    for a, b, name in zip(stored, recomputed, ("o", "rem", "dq", "dk", "dv")):
+        assert H.rel_l2(a, b) <= 4e-3, name
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_varlen_forms_agree(sb, cuda_device, dtype):
     """zero_start / int32 / missing max_seqlens / empty sequences are the same computation."""
