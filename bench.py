@@ -43,7 +43,7 @@ if ROOT not in sys.path:
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
 # profiles/tc_kernels_c2_ncu.md (workload c2 only; other workloads report null)
-NCU_TRAFFIC_BYTES = {"c2": {"fwd": 481.0e6, "bwd_dq": 381.6e6, "bwd_dkv": 451.5e6}}
+NCU_TRAFFIC_BYTES = {"c2": {"fwd": 495.8e6, "bwd_dq": 1462.0e6, "bwd_dkv": 1402.4e6}}
 
 
 # ---------------------------------------------------------------------------------------------------
