@@ -108,3 +108,17 @@ def test_dropin_alias():
     assert sb_attn_varlen is sb.sb_attn_varlen and sb_attn is sb.sb_attn
     for key in [k for k in sys.modules if k.startswith("stickbreaking_attention_alias_for_test")]:
         del sys.modules[key]
+
+
+def test_benchmark_sweep_host_side():
+    """Rotary tables of the FlashAttention comparator and the no-device refusal of the sweep."""
+    import pytest
+    from stickbreaking_attention_b200 import benchmarks
+    cos, sin = benchmarks._rope_tables(torch.arange(5), 8, torch.float32)
+    assert cos.shape == (5, 8) and torch.allclose(cos[0], torch.ones(8)) and torch.allclose(sin[0], torch.zeros(8))
+    x = torch.randn(5, 8)
+    rot = x * cos + benchmarks._rotate_half(x) * sin            # a rotation: norms of the (i, i+4) pairs are kept
+    assert torch.allclose(rot[:, :4] ** 2 + rot[:, 4:] ** 2, x[:, :4] ** 2 + x[:, 4:] ** 2, atol=1e-5)
+    if not torch.cuda.is_available():
+        with pytest.raises(SystemExit):
+            benchmarks.main(["--op", "attn", "--lengths", "256"])
