@@ -65,12 +65,18 @@ enum SbFlags {
   SB_FLAG_BWD_SKIP_DKV = 4, /* timing aid: sb_bwd enqueues only the dQ kernel                   */
   SB_FLAG_BWD_SKIP_DQ = 8,  /* timing aid: sb_bwd enqueues only the dK/dV kernel, which then reads
                             what a previous full sb_bwd left in the same workspace              */
-  SB_FLAG_BWD_RECOMPUTE = 16 /* small-workspace backward.  By default (16-bit tensors, head_dim 72..128)
+  SB_FLAG_BWD_RECOMPUTE = 16, /* small-workspace backward.  By default (16-bit tensors, head_dim 72..128)
                             the dQ kernel stores its A and dz tiles -- 64 KiB per (query tile, key tile)
                             pair and head, heads processed in chunks of at most 8 GiB -- and the dK/dV
                             kernel is two plain GEMMs over them.  With this flag, or when one head
                             exceeds 8 GiB, the dK/dV kernel recomputes the tiles from boundary values
                             (a few KiB per pair).  Same 16-bit tiles either way.                 */
+  SB_FLAG_FUSE_REM_V = 32   /* the caller wants out = o + rem[..., None] * v, what every caller of the
+                            reference computes right after the operator (tests/test_varlen.py:101,
+                            tests/test_attn.py:64).  sb_fwd writes `out` to `o` (rem and log_rem as usual).
+                            sb_bwd takes d_out in `d_o`, adds <d_out, v> per row to d_rem (which may then be
+                            NULL = zero) and rem * d_out to dv, and needs 4 more workspace bytes per
+                            (batch, head, token).                                                  */
 };
 
 typedef struct SbTensor {

@@ -26,6 +26,7 @@ static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; 
 //   packed batches: [order int2 x tiles][order2 (backward) int2 x tiles]
 //   backward, either: [A | dz tiles, 16-bit x chunk_heads x pairs_cap x 2 x 128 x 128]   (stored-tiles mode)
 //             or:     [R1 fp32 x chunk_heads x pairs_cap x halves x tile][S2 same]       (recompute mode)
+//   backward with SB_FLAG_FUSE_REM_V: [d_rem + <d_out, v>, fp32 x batch x heads x tokens]
 struct Plan {
   int path;
   int tile;
@@ -33,7 +34,7 @@ struct Plan {
   int n_max;
   int max_seqlen;
   long long pairs_cap;
-  size_t off_tile_prefix, off_pair_prefix, off_order, off_order2, off_bnd;
+  size_t off_tile_prefix, off_pair_prefix, off_order, off_order2, off_bnd, off_drem;
   int bnd_halves;             // boundary records per (query tile, key tile) pair
   size_t bnd_bytes_per_head;  // one of the two arrays
   int chunk_heads;
@@ -115,7 +116,10 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   pl.chunk_heads = (int)chunk;
   const size_t trace_bytes = (p->reserved & 0x100) ? kTraceBytes : 0;   // experiments only
   pl.total_fwd = pl.off_bnd + trace_bytes;
-  pl.total_bwd = pl.off_bnd + per_head * chunk + trace_bytes;
+  pl.off_drem = align_up(pl.off_bnd + per_head * chunk, 256);
+  const size_t drem_bytes =
+      (p->flags & SB_FLAG_FUSE_REM_V) ? align_up(sizeof(float) * (size_t)p->batch * p->heads * (size_t)T, 256) : 0;
+  pl.total_bwd = pl.off_drem + drem_bytes + trace_bytes;
   return SB_OK;
 }
 
@@ -154,7 +158,7 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
     if ((rc = check_tensor(p->d_o, "d_o", true)) || (rc = check_tensor(p->dq, "dq", true)) ||
         (rc = check_tensor(p->dk, "dk", true)) || (rc = check_tensor(p->dv, "dv", true)))
       return rc;
-    if (p->d_rem == nullptr) return fail(SB_ERR_ARGUMENT, "d_rem is NULL");
+    if (p->d_rem == nullptr && !(p->flags & SB_FLAG_FUSE_REM_V)) return fail(SB_ERR_ARGUMENT, "d_rem is NULL");
   }
   const size_t need = backward ? pl.total_bwd : pl.total_fwd;
   if (p->workspace == nullptr || p->workspace_bytes < need)
@@ -199,6 +203,8 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
     k.bnd_s2 = reinterpret_cast<float *>(ws + pl.off_bnd + pl.bnd_bytes_per_head * pl.chunk_heads);
   }
   k.pairs_cap = pl.pairs_cap;
+  k.fuse_rem_v = (p->flags & SB_FLAG_FUSE_REM_V) ? 1 : 0;
+  if (backward && k.fuse_rem_v) k.drem_f32 = reinterpret_cast<float *>(ws + pl.off_drem);
   k.status = p->status;
   return SB_OK;
 }
@@ -217,6 +223,11 @@ static int run(const SbParams *p, void *stream, bool backward) {
   cudaError_t e = launch_prep(k, s);
   g_launches += (p->cu_seqlens != nullptr && k.trace != nullptr) ? 2 : 1;   // prep kernel or header clear (both with the event log)
   if (e != cudaSuccess) return fail(SB_ERR_CUDA, "prep launch: %s", cudaGetErrorString(e));
+  if (backward && k.fuse_rem_v) {
+    e = launch_fused_drem(k, p->dtype, s);
+    g_launches += 1;
+    if (e != cudaSuccess) return fail(SB_ERR_CUDA, "d_rem launch: %s", cudaGetErrorString(e));
+  }
   const int chunk = backward ? pl.chunk_heads : p->heads;
   for (int h0 = 0; h0 < p->heads; h0 += chunk) {
     k.head0 = h0;
@@ -231,6 +242,11 @@ static int run(const SbParams *p, void *stream, bool backward) {
       g_launches += 1;
       if (e != cudaSuccess) return fail(SB_ERR_CUDA, "tail launch: %s", cudaGetErrorString(e));
     }
+  }
+  if (backward && k.fuse_rem_v && !k.skip_dkv) {
+    e = launch_fused_dv(k, p->dtype, s);
+    g_launches += 1;
+    if (e != cudaSuccess) return fail(SB_ERR_CUDA, "dv launch: %s", cudaGetErrorString(e));
   }
   return SB_OK;
 }

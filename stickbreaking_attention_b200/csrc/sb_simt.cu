@@ -173,6 +173,61 @@ __global__ void zero_tail_kernel(KParams p, bool backward) {
   }
 }
 
+// Backward with out = o + rem * v: the upstream gradient of rem gains <d_out, v> per row.  One warp per row of the
+// (batch, heads, tokens) array; rows that belong to no sequence are never read by the kernels and get 0.
+template <typename T>
+__global__ void __launch_bounds__(256) fused_drem_kernel(KParams p) {
+  const long long rows = (long long)p.batch * p.heads * p.tokens;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long tok = row % p.tokens, bh = row / p.tokens;
+  const long long h = bh % p.heads, b = bh / p.heads;
+  const T *g = reinterpret_cast<const T *>(p.d_o.ptr) + b * p.d_o.sb + h * p.d_o.sh + tok * p.d_o.st;
+  const T *v = reinterpret_cast<const T *>(p.v.ptr) + b * p.v.sb + h * p.v.sh + tok * p.v.st;
+  float s = 0.f;
+  for (int x = lane; x < p.head_dim; x += 32) s = fmaf(to_f32<T>(g[x]), to_f32<T>(v[x]), s);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) p.drem_f32[row] = s + (p.d_rem != nullptr ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[row]) : 0.f);
+}
+
+cudaError_t launch_fused_drem(const KParams &p, int dtype, cudaStream_t s) {
+  const long long rows = (long long)p.batch * p.heads * p.tokens;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype == SB_DTYPE_F32) fused_drem_kernel<float><<<grid, 256, 0, s>>>(p);
+  else if (dtype == SB_DTYPE_BF16) fused_drem_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
+  else fused_drem_kernel<__half><<<grid, 256, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+// ... and dv gains rem * d_out on the rows that belong to a sequence (rem = 2^log_rem, from the saved fp64 value).
+template <typename T>
+__global__ void __launch_bounds__(256) fused_dv_kernel(KParams p) {
+  if (p.hdr[0]) return;
+  const long long covered = p.cu != nullptr ? (long long)p.hdr[1] : p.tokens;
+  const long long rows = (long long)p.batch * p.heads * p.tokens;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long tok = row % p.tokens, bh = row / p.tokens;
+  if (tok >= covered) return;
+  const long long h = bh % p.heads, b = bh / p.heads;
+  const T *g = reinterpret_cast<const T *>(p.d_o.ptr) + b * p.d_o.sb + h * p.d_o.sh + tok * p.d_o.st;
+  T *dv = reinterpret_cast<T *>(p.dv.ptr) + b * p.dv.sb + h * p.dv.sh + tok * p.dv.st;
+  const float rem = exp2f((float)p.log_rem[row]);
+  for (int x = lane; x < p.head_dim; x += 32) dv[x] = from_f32<T>(fmaf(rem, to_f32<T>(g[x]), to_f32<T>(dv[x])));
+}
+
+cudaError_t launch_fused_dv(const KParams &p, int dtype, cudaStream_t s) {
+  const long long rows = (long long)p.batch * p.heads * p.tokens;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype == SB_DTYPE_F32) fused_dv_kernel<float><<<grid, 256, 0, s>>>(p);
+  else if (dtype == SB_DTYPE_BF16) fused_dv_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
+  else fused_dv_kernel<__half><<<grid, 256, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_zero_tail(const KParams &p, int dtype, bool backward, cudaStream_t s) {
   if (p.cu == nullptr) return cudaSuccess;
   dim3 grid(8, p.head_cnt);
@@ -269,12 +324,18 @@ __global__ void __launch_bounds__(256) simt_fwd_kernel(KParams p) {
   }
 
   const int gi = I * kT + r;
+  if (p.fuse_rem_v) {   // out = o + rem * v: the row owners publish rem through the free score tile
+    if (t < kT) Ss[t * kLdS] = expf(-run_sp);
+    __syncthreads();
+  }
   if (gi < c.len) {
     T *o = reinterpret_cast<T *>(p.o.ptr) + c.boff * p.o.sb + (long long)h * p.o.sh + (c.tok0 + gi) * p.o.st;
+    const T *vrow = reinterpret_cast<const T *>(p.v.ptr) + c.boff * p.v.sb + (long long)h * p.v.sh + (c.tok0 + gi) * p.v.st;
+    const float rem_r = p.fuse_rem_v ? Ss[r * kLdS] : 0.f;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int x = cg + 8 * u;
-      if (x < d) o[x] = from_f32<T>(acc[u]);
+      if (x < d) o[x] = from_f32<T>(p.fuse_rem_v ? fmaf(rem_r, to_f32<T>(vrow[x]), acc[u]) : acc[u]);
     }
   }
   if (t < kT && I * kT + t < c.len) {
@@ -333,7 +394,7 @@ __global__ void __launch_bounds__(256) simt_bwd_dq_kernel(KParams p) {
   if (t < kT && my_row < c.len) {
     const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + my_row;
     r1 = p.log_rem[idx] * kLn2D;
-    dr = to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]);
+    dr = load_drem<T>(p, idx);
   }
 
   for (int J = 0; J <= I; ++J) {
@@ -406,7 +467,7 @@ __global__ void __launch_bounds__(256) simt_bwd_dkv_kernel(KParams p) {
       const int gi = I * kT + t;
       float dr = 0.f;
       if (gi < c.len)
-        dr = to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]);
+        dr = load_drem<T>(p, (c.boff * p.heads + h) * p.tokens + c.tok0 + gi);
       const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * kT + t;
       float sp_sum, g_sum;
       bwd_row_pass(Zs, Ps, t, gi, J, c.len, p.attend_current, p.bnd_r1[slot], p.bnd_s2[slot], dr, sp_sum, g_sum);

@@ -287,7 +287,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const bool valid = gi < c.len;
     const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + gi;
     double r1 = valid ? p.log_rem[idx] : 0.0;   // sum of log2(1-beta) over the keys from the current tile on
-    const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]) : 0.f;
+    const float dr = valid ? load_drem<T>(p, idx) : 0.f;
     float gpre = 0.f;
     // boundary records: [pair][half: keys 0.. / keys 64..][row]
     const long long slot0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (4 * kBM) + r;
@@ -468,8 +468,7 @@ tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * (4 * kBM) + r;
       const float r1f = p.bnd_r1[slot];
       const float gpre = p.bnd_s2[slot];
-      const float dr = valid ? to_f32<T>(reinterpret_cast<const T *>(
-                                   p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
+      const float dr = valid ? load_drem<T>(p, (c.boff * p.heads + h) * p.tokens + c.tok0 + gi) : 0.f;
       ok = wait_or_abort(bar(vSpFull), i & 1, abort_flag, p, 230);
       if (ok && i > 0) ok = wait_or_abort(bar(vAzEmpty), (i - 1) & 1, abort_flag, p, 231);
       if (!ok) break;
@@ -736,7 +735,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const bool valid = gi < c.len;
     const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + gi;
     double r1 = (valid && my_steps > 0) ? p.log_rem[idx] : 0.0;   // sum of log2(1-beta) over the keys from the current one on
-    const float dr = (valid && my_steps > 0) ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]) : 0.f;
+    const float dr = (valid && my_steps > 0) ? load_drem<T>(p, idx) : 0.f;
     float gpre = 0.f;
     uint8_t *gZ = gbase + (sZ - base) + w * kZBytes;
     const uint32_t tS = tmem + w * 128 + lane_off, tP = tS + 64;
@@ -1018,7 +1017,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 4 + quarter) * kBM + r;
       r1f = p.bnd_r1[slot];
       gpre = p.bnd_s2[slot];
-      dr = gi < c.len ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[(c.boff * p.heads + h) * p.tokens + c.tok0 + gi]) : 0.f;
+      dr = gi < c.len ? load_drem<T>(p, (c.boff * p.heads + h) * p.tokens + c.tok0 + gi) : 0.f;
     };
     uint8_t *gA = gbase + (sAZ - base);
     uint8_t *gZ = gA + kAzBytes;

@@ -94,9 +94,27 @@ __device__ __forceinline__ void store_packed_global16(unsigned short *dst, const
                : "memory");   // one full 32-byte sector per thread
 }
 
+// Eight consecutive 16-bit values of a global row (16 bytes, aligned) as floats.
+template <bool kFp16>
+__device__ __forceinline__ void load_row8(const void *src, float (&x)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4 *>(src);
+  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (kFp16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[i]));
+      x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    } else {
+      x[2 * i] = __uint_as_float(u[i] << 16); x[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  }
+}
+
 // TMEM accumulator rows (one per thread) -> 16-bit global rows, `mul` applied, columns >= head_dim dropped.
+// With `add_row` (a 16-bit global row of head_dim values) the stored value is acc * mul + add_mul * add_row.
 template <int D, bool kFp16, typename T>
-__device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool valid, int head_dim, float mul) {
+__device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool valid, int head_dim, float mul,
+                                               const T *add_row = nullptr, float add_mul = 0.f) {
 #pragma unroll 1
   for (int ch = 0; ch < D / 32; ++ch) {
     uint32_t v[32];
@@ -107,11 +125,20 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool
       for (int g = 0; g < 4; ++g) {
         const int x0 = ch * 32 + g * 8;
         if (x0 < head_dim) {
+          float x[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = __uint_as_float(v[g * 8 + i]) * mul;
+          if (add_row != nullptr) {
+            float a[8];
+            load_row8<kFp16>(add_row + x0, a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = fmaf(add_mul, a[i], x[i]);
+          }
           uint4 w;
-          w.x = pack2<kFp16>(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
-          w.y = pack2<kFp16>(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
-          w.z = pack2<kFp16>(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
-          w.w = pack2<kFp16>(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
+          w.x = pack2<kFp16>(x[0], x[1]);
+          w.y = pack2<kFp16>(x[2], x[3]);
+          w.z = pack2<kFp16>(x[4], x[5]);
+          w.w = pack2<kFp16>(x[6], x[7]);
           *reinterpret_cast<uint4 *>(grow + x0) = w;
         }
       }
@@ -121,8 +148,10 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, T *grow, bool
 
 // TMEM accumulator rows (one per thread) -> a 16-bit [128 x D] tile in shared memory (D / 64 blocks of 128-byte
 // rows, 128-byte swizzle), from where TMA stores it with full lines instead of 16 bytes per thread and row.
+// `add_row` / `add_mul` as above (the row must exist: callers use this for full tiles only).
 template <int D, bool kFp16>
-__device__ __forceinline__ void stage_acc_rows(uint32_t tmem_addr, uint8_t *tile, int r, float mul) {
+__device__ __forceinline__ void stage_acc_rows(uint32_t tmem_addr, uint8_t *tile, int r, float mul,
+                                               const void *add_row = nullptr, float add_mul = 0.f, int head_dim = D) {
 #pragma unroll 1
   for (int ch = 0; ch < D / 32; ++ch) {
     uint32_t v[32];
@@ -131,6 +160,17 @@ __device__ __forceinline__ void stage_acc_rows(uint32_t tmem_addr, uint8_t *tile
     float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]) * mul;
+    if (add_row != nullptr) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (ch * 32 + g * 8 < head_dim) {
+          float a[8];
+          load_row8<kFp16>(reinterpret_cast<const uint16_t *>(add_row) + ch * 32 + g * 8, a);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[g * 8 + i] = fmaf(add_mul, a[i], x[g * 8 + i]);
+        }
+      }
+    }
     store_row_chunk<kFp16>(tile, r, ch * 32, x);
   }
 }

@@ -321,10 +321,15 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc_fence_after();
         const bool valid = row < w.c.len;
         const int tile_row0 = w.blk_row0 + wg * kBM;
+        const float rem_f = ex2(-(float)run);
+        // out = o + rem * v on request: this row of V comes straight from global memory
+        const T *vrow = (p.fuse_rem_v && valid) ? reinterpret_cast<const T *>(p.v.ptr) + w.c.boff * p.v.sb +
+                                                      (long long)w.h * p.v.sh + (w.c.tok0 + row) * p.v.st
+                                                : nullptr;
         if (tile_row0 + kBM <= w.c.len) {
           // full tile: through this tile's two P buffers (all P V MMAs are done), one TMA store per warp and half
           uint8_t *stage = gP + wg * 2 * kPBytes;
-          stage_acc_rows<D, kFp16>(tmem + 256 + wg * 128 + lane_off, stage, r, 1.f);
+          stage_acc_rows<D, kFp16>(tmem + 256 + wg * 128 + lane_off, stage, r, 1.f, vrow, rem_f, p.head_dim);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -336,11 +341,11 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         } else {
           // the sequence ends inside the tile: row by row, rows past the end are left alone
           T *orow = reinterpret_cast<T *>(p.o.ptr) + w.c.boff * p.o.sb + (long long)w.h * p.o.sh + (w.c.tok0 + row) * p.o.st;
-          store_acc_rows<D, kFp16, T>(tmem + 256 + wg * 128 + lane_off, orow, valid, p.head_dim, 1.f);
+          store_acc_rows<D, kFp16, T>(tmem + 256 + wg * 128 + lane_off, orow, valid, p.head_dim, 1.f, vrow, rem_f);
         }
         if (valid) {
           const long long idx = (w.c.boff * p.heads + w.h) * p.tokens + w.c.tok0 + row;
-          reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(ex2(-(float)run));
+          reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(rem_f);
           p.log_rem[idx] = -run;
         }
       }

@@ -95,7 +95,8 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     return t if ok else t.contiguous()
 
 
-def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero):
+def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero,
+          fuse_rem_v=False):
     _require(q.is_cuda, "stick-breaking attention runs on a CUDA device only (no CPU path)")
     _require(q.dtype in _cabi.SB_DTYPE, f"unsupported dtype {q.dtype}")
     _require(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype")
@@ -121,7 +122,8 @@ def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_c
     prm.logit_scale = float(logit_scale)
     prm.flags = (_cabi.SB_FLAG_FORCE_SIMT if _state["force_simt"] else 0) | \
                 (_cabi.SB_FLAG_BWD_RECOMPUTE if _state["bwd_recompute"] else 0) | \
-                (_cabi.SB_FLAG_CHECK_LEADING_ZERO if leading_zero else 0)
+                (_cabi.SB_FLAG_CHECK_LEADING_ZERO if leading_zero else 0) | \
+                (_cabi.SB_FLAG_FUSE_REM_V if fuse_rem_v else 0)
     prm.q = _cabi.tensor_arg(q, fixed)
     prm.k = _cabi.tensor_arg(k, fixed)
     prm.v = _cabi.tensor_arg(v, fixed)
@@ -146,10 +148,10 @@ def _run(backward: bool, prm, device):
 
 
 def _fwd_impl(fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero,
-              o, rem, log_rem):
+              o, rem, log_rem, fuse_rem_v=False):
     prm = _cabi.SbParams()
     _fill(prm, fixed=fixed, q=q, k=k, v=v, cu_seqlens=cu_seqlens, max_seqlens=max_seqlens,
-          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero)
+          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero, fuse_rem_v=fuse_rem_v)
     prm.o = _cabi.tensor_arg(o, fixed)
     prm.rem = rem.data_ptr()
     prm.log_rem = log_rem.data_ptr()
@@ -157,13 +159,13 @@ def _fwd_impl(fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_curre
 
 
 def _bwd_impl(fixed, do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current,
-              leading_zero, dq, dk, dv):
+              leading_zero, dq, dk, dv, fuse_rem_v=False):
     prm = _cabi.SbParams()
     _fill(prm, fixed=fixed, q=q, k=k, v=v, cu_seqlens=cu_seqlens, max_seqlens=max_seqlens,
-          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero)
+          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero, fuse_rem_v=fuse_rem_v)
     prm.log_rem = log_rem.data_ptr()
     prm.d_o = _cabi.tensor_arg(do, fixed)
-    prm.d_rem = dr.data_ptr()
+    prm.d_rem = dr.data_ptr() if dr is not None else None
     prm.dq = _cabi.tensor_arg(dq, fixed)
     prm.dk = _cabi.tensor_arg(dk, fixed)
     prm.dv = _cabi.tensor_arg(dv, fixed)
@@ -267,6 +269,34 @@ def attn_bwd(do, dr, q, k, v, log_rem, logit_scale: float, attend_current: bool 
         _op_attn_bwd(do, dr, q, k, v, log_rem, float(logit_scale), bool(attend_current), dq, dk, dv)
     else:
         _bwd_impl(True, do, dr, q, k, v, None, None, log_rem, logit_scale, attend_current, False, dq, dk, dv)
+    return dq, dk, dv
+
+
+def fused_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, leading_zero=False):
+    """Forward with the callers' usual next step folded in: returns ``(out, rem, log_rem)`` with
+    ``out = o + rem[..., None] * v`` (``tests/test_varlen.py:101``, ``tests/test_attn.py:64`` of the reference).
+    Fixed-length when ``cu_seqlens`` is None.  Always a direct call of the C ABI (``SB_FLAG_FUSE_REM_V``)."""
+    fixed = cu_seqlens is None
+    q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+    out = torch.empty_like(q)
+    rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
+    log_rem = torch.empty(q.shape[:-1], dtype=torch.float64, device=q.device)
+    ends = None if fixed else _strip(cu_seqlens, leading_zero)
+    _fwd_impl(fixed, q, k, v, ends, max_seqlens, logit_scale, attend_current, leading_zero and not fixed, out, rem,
+              log_rem, fuse_rem_v=True)
+    return out, rem, log_rem
+
+
+def fused_bwd(dout, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current=False,
+              leading_zero=False):
+    """Backward of ``fused_fwd``'s ``out``: ``<d_out, v>`` goes into the gradient of rem and ``rem * d_out`` into dv
+    inside the library; returns ``(dq, dk, dv)``."""
+    fixed = cu_seqlens is None
+    q, k, v, dout = _tma_ready(q), _tma_ready(k), _tma_ready(v), _tma_ready(dout.to(q.dtype))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ends = None if fixed else _strip(cu_seqlens, leading_zero)
+    _bwd_impl(fixed, dout, None, q, k, v, ends, max_seqlens, log_rem, logit_scale, attend_current,
+              leading_zero and not fixed, dq, dk, dv, fuse_rem_v=True)
     return dq, dk, dv
 
 

@@ -39,3 +39,28 @@ def sb_attn(q, k, v, inv_temp=None, zero_start=True, attend_current=False):
 
 def sb_attn_(q, k, v, inv_temp, attend_current):
     return StickBreakingAttention.apply(q, k, v, inv_temp, attend_current)
+
+
+class StickBreakingAttentionFused(torch.autograd.Function):
+    """``out = o + rem[..., None] * v`` in one operator, fixed-length batch."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, inv_temp, attend_current=False):
+        out, _, log_rem = ops.fused_fwd(q, k, v, None, None, inv_temp, attend_current=attend_current)
+        ctx.save_for_backward(q, k, v, log_rem)
+        ctx.args = (inv_temp, attend_current)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, log_rem = ctx.saved_tensors
+        inv_temp, attend_current = ctx.args
+        dq, dk, dv = ops.fused_bwd(dout, q, k, v, None, None, log_rem, inv_temp, attend_current=attend_current)
+        return dq, dk, dv, None, None
+
+
+def sb_attn_fused(q, k, v, inv_temp=None, zero_start=True, attend_current=False):
+    """Same arguments as ``sb_attn``; returns ``o + rem[..., None] * v`` (``tests/test_attn.py:64`` of the reference)."""
+    if inv_temp is None:
+        inv_temp = 1 / math.sqrt(q.size(-1))
+    return StickBreakingAttentionFused.apply(q, k, v, inv_temp, attend_current)

@@ -54,3 +54,33 @@ def sb_attn_varlen(q, k, v, cu_seqlens, max_seqlens=None, inv_temp=None, zero_st
 def sb_attn_varlen_(q, k, v, inv_temp, cu_seqlens, max_seqlens, attend_current, leading_zero=False):
     return StickBreakingAttention.apply(q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current,
                                         leading_zero)
+
+
+class StickBreakingAttentionFused(torch.autograd.Function):
+    """``out = o + rem[..., None] * v`` in one operator (forward epilogue and backward fold inside the kernels' C ABI)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current, leading_zero):
+        out, _, log_rem = ops.fused_fwd(q, k, v, cu_seqlens, max_seqlens, inv_temp,
+                                        attend_current=attend_current, leading_zero=leading_zero)
+        ctx.save_for_backward(q, k, v, log_rem, cu_seqlens)
+        ctx.args = (max_seqlens, inv_temp, attend_current, leading_zero)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, log_rem, cu_seqlens = ctx.saved_tensors
+        max_seqlens, inv_temp, attend_current, leading_zero = ctx.args
+        dq, dk, dv = ops.fused_bwd(dout, q, k, v, cu_seqlens, max_seqlens, log_rem, inv_temp,
+                                   attend_current=attend_current, leading_zero=leading_zero)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def sb_attn_varlen_fused(q, k, v, cu_seqlens, max_seqlens=None, inv_temp=None, zero_start=True,
+                         attend_current=False):
+    """Same arguments as ``sb_attn_varlen``; returns the single tensor ``o + rem[..., None] * v`` that the reference's
+    callers compute from its two outputs (``tests/test_varlen.py:101``), without the extra passes over o and v."""
+    if inv_temp is None:
+        inv_temp = 1 / math.sqrt(q.size(-1))
+    return StickBreakingAttentionFused.apply(q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current,
+                                             bool(zero_start))

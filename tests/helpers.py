@@ -81,3 +81,35 @@ def assert_parity(got, want, dtype, what=""):
     for name in ("dq", "dk", "dv"):
         assert report[name][1] <= tol["grad_rel"], f"{what}: {name} rel-L2 {report[name][1]:.3e} > {tol['grad_rel']}"
     return report
+
+
+def oracle_fused(q, k, v, dout, cu=None, **kw):
+    """Oracle for out = o + rem[..., None] * v (what the reference's callers compute, tests/test_varlen.py:101) and
+    the gradients of q, k, v for an upstream gradient of `out`: d_o = d_out, d_rem = <d_out, v>, dv += rem * d_out."""
+    vf, gf = v.float(), dout.float()
+    drem = (gf * vf).sum(-1)
+    if cu is None:
+        o, rem, dq, dk, dv = oracle_fixed(q, k, v, gf, drem, **kw)
+    else:
+        o, rem, dq, dk, dv = oracle_varlen(q, k, v, gf, drem, cu, **kw)
+    return o + rem[..., None] * vf, dq, dk, dv + rem[..., None] * gf
+
+
+def run_fused(sb, q, k, v, dout, device, cu=None, **kw):
+    qd, kd, vd = (t.to(device).requires_grad_(True) for t in (q, k, v))
+    if cu is None:
+        out = sb.sb_attn_fused(qd, kd, vd, **kw)
+    else:
+        out = sb.sb_attn_varlen_fused(qd, kd, vd, cu.to(device), **kw)
+    dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), dout.to(device))
+    return tuple(t.detach().cpu() for t in (out, dq, dk, dv))
+
+
+def assert_fused_parity(got, want, dtype, what=""):
+    tol = TOL[dtype]
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        assert torch.isfinite(a.float()).all(), f"{what}: {name} has non-finite values"
+        if name == "out":
+            assert max_abs(a, b) <= tol["out"], f"{what}: out max-abs {max_abs(a, b):.3e} > {tol['out']}"
+        else:
+            assert rel_l2(a, b) <= tol["grad_rel"], f"{what}: {name} rel-L2 {rel_l2(a, b):.3e} > {tol['grad_rel']}"

@@ -119,6 +119,50 @@ def test_backward_modes_agree(sb, cuda_device):
         assert H.rel_l2(a, b) <= 4e-3, name
 
 
+@pytest.mark.parametrize("ac", [False, True])
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 128), (torch.bfloat16, 64), (torch.float16, 96),
+                                     (torch.bfloat16, 50), (torch.float32, 64)])
+def test_fused_rem_v_varlen(sb, cuda_device, dtype, d, ac):
+    """out = o + rem * v in one operator (forward epilogue, backward fold) against the oracle's o, rem and gradients
+    combined on the CPU; N(0, 0.5^2) inputs keep |out| below 2, where a bf16 step is still inside the bound."""
+    lengths = [300, 1, 129, 700, 64, 257]
+    q, k, v, dout, _ = H.make_inputs((3, sum(lengths), d), dtype, seed=20 + d, std=0.5)
+    cu = cu_of(lengths, True)
+    got = H.run_fused(sb, q, k, v, dout, cuda_device, cu, max_seqlens=max(lengths), zero_start=True,
+                      attend_current=ac)
+    want = H.oracle_fused(q, k, v, dout, cu, zero_start=True, attend_current=ac)
+    H.assert_fused_parity(got, want, dtype, "fused varlen")
+
+
+def test_fused_rem_v_matches_unfused_and_leaves_tail_zero(sb, cuda_device):
+    """The fused operator against the two-output operator followed by the callers' arithmetic, both modes of the
+    backward, with tokens past the last sequence end (their rows of out and of the gradients stay zero)."""
+    lengths, total = [500, 130, 1000], 1700
+    q, k, v, dout, _ = H.make_inputs((2, total, 128), torch.bfloat16, seed=31, std=0.5)
+    cu = cu_of(lengths)
+    want = H.oracle_fused(q[:, :1630], k[:, :1630], v[:, :1630], dout[:, :1630], cu)
+    for small in (False, True):
+        with sb.small_backward_workspace(small):
+            got = H.run_fused(sb, q, k, v, dout, cuda_device, cu, max_seqlens=1000, zero_start=False)
+        H.assert_fused_parity([t[:, :1630] for t in got], want, torch.bfloat16, f"fused small={small}")
+        for t in got:
+            assert torch.all(t[:, 1630:] == 0)
+    qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k, v))
+    o, rem = sb.sb_attn_varlen(qd, kd, vd, cu.to(cuda_device), 1000, zero_start=False)
+    out2 = o + rem[..., None] * vd
+    grads2 = torch.autograd.grad(out2, (qd, kd, vd), dout.to(cuda_device))
+    for a, b in zip(got, (out2,) + grads2):
+        assert H.rel_l2(a[:, :1630], b.detach().cpu()[:, :1630]) <= 1e-2
+
+
+@pytest.mark.parametrize("shape,dtype", [((2, 3, 384, 128), torch.bfloat16), ((1, 2, 300, 64), torch.float16),
+                                         ((1, 2, 200, 32), torch.float32)])
+def test_fused_rem_v_fixed(sb, cuda_device, shape, dtype):
+    q, k, v, dout, _ = H.make_inputs(shape, dtype, seed=41, std=0.5)
+    got = H.run_fused(sb, q, k, v, dout, cuda_device)
+    H.assert_fused_parity(got, H.oracle_fused(q, k, v, dout), dtype, "fused fixed")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_varlen_forms_agree(sb, cuda_device, dtype):
     """zero_start / int32 / missing max_seqlens / empty sequences are the same computation."""
