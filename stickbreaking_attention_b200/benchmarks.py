@@ -7,6 +7,7 @@ k because stick-breaking attention needs none.  Timing is by CUDA events (median
 
     python -m stickbreaking_attention_b200.benchmarks --op varlen
     python -m stickbreaking_attention_b200.benchmarks --op attn --fwd-only
+    python -m stickbreaking_attention_b200.benchmarks --op fused --batch 8 --heads 16 --lengths 2048
 
 Rows printed: length, ms of this package, ms of FlashAttention-2 (or why it is unavailable), ms of the reference's
 Triton operator when a `stickbreaking_attention` package that is not this one can be imported and compiles here.
@@ -127,6 +128,30 @@ def bench_varlen(length, batch, heads, dim, dtype, bwd, warmup, rep):
             "reference_triton_ms": _try("reference", reference, warmup, max(rep // 4, 1))}
 
 
+def bench_fused(length, batch, heads, dim, dtype, bwd, warmup, rep):
+    """`o + rem[..., None] * v` (the step every caller of the reference takes next, `tests/test_varlen.py:101`):
+    the two-output operator followed by torch arithmetic, against the fused operator."""
+    from . import sb_attn_varlen, sb_attn_varlen_fused
+    dev = torch.device("cuda:0")
+    torch.manual_seed(1337)
+    total = batch * length
+    q, k, v = (torch.randn(heads, total, dim, device=dev, dtype=dtype).requires_grad_() for _ in range(3))
+    do = torch.randn(heads, total, dim, device=dev, dtype=dtype)
+    ends = torch.arange(1, batch + 1, device=dev, dtype=torch.int32) * length
+
+    def two_step():
+        def f():
+            o, rem = sb_attn_varlen(q, k, v, ends, length, zero_start=False)
+            return o + rem[..., None] * v
+        return _with_backward(f, (q, k, v), do, bwd)
+
+    def fused():
+        return _with_backward(lambda: sb_attn_varlen_fused(q, k, v, ends, length, zero_start=False), (q, k, v), do, bwd)
+
+    return {"length": length, "sb_b200_ms": _try("fused", fused, warmup, rep),
+            "two_step_ms": _try("two_step", two_step, warmup, rep)}
+
+
 def bench_attn(length, batch, heads, dim, dtype, bwd, warmup, rep):
     from . import sb_attn
     dev = torch.device("cuda:0")
@@ -171,7 +196,7 @@ def bench_attn(length, batch, heads, dim, dtype, bwd, warmup, rep):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("--op", choices=("varlen", "attn"), default="varlen")
+    ap.add_argument("--op", choices=("varlen", "attn", "fused"), default="varlen")
     ap.add_argument("--lengths", type=int, nargs="+", default=[4096, 8192, 12288, 16384])
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--heads", type=int, default=12)
@@ -182,7 +207,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         sys.exit("benchmarks need a CUDA device")
-    fn = bench_varlen if a.op == "varlen" else bench_attn
+    fn = {"varlen": bench_varlen, "attn": bench_attn, "fused": bench_fused}[a.op]
     flop_c = 2 if a.fwd_only else 7
     for length in a.lengths:
         row = fn(length, a.batch, a.heads, a.head_dim, torch.bfloat16, not a.fwd_only, a.warmup, a.rep)

@@ -173,59 +173,105 @@ __global__ void zero_tail_kernel(KParams p, bool backward) {
   }
 }
 
-// Backward with out = o + rem * v: the upstream gradient of rem gains <d_out, v> per row.  One warp per row of the
-// (batch, heads, tokens) array; rows that belong to no sequence are never read by the kernels and get 0.
-template <typename T>
-__global__ void __launch_bounds__(256) fused_drem_kernel(KParams p) {
-  const long long rows = (long long)p.batch * p.heads * p.tokens;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const long long tok = row % p.tokens, bh = row / p.tokens;
-  const long long h = bh % p.heads, b = bh / p.heads;
-  const T *g = reinterpret_cast<const T *>(p.d_o.ptr) + b * p.d_o.sb + h * p.d_o.sh + tok * p.d_o.st;
-  const T *v = reinterpret_cast<const T *>(p.v.ptr) + b * p.v.sb + h * p.v.sh + tok * p.v.st;
+// Backward with out = o + rem * v: the upstream gradient of rem gains <d_out, v> per row, and dv gains rem * d_out
+// (rem = 2^log_rem, from the saved fp64 value) on the rows that belong to a sequence.  Two elementwise kernels over
+// the (batch, heads, tokens) rows: grid (token blocks, heads, batch); `group` consecutive lanes share a row, each
+// lane holding `kVec` consecutive elements (16 bytes when the rows allow it, else one element).
+template <typename T, int kVec>
+struct alignas(16) RowVec {
+  T e[kVec];
+};
+template <typename T, int kVec>
+__device__ __forceinline__ RowVec<T, kVec> load_vec(const T *src) {
+  RowVec<T, kVec> r;
+  if (kVec == 1) r.e[0] = *src;
+  else *reinterpret_cast<uint4 *>(&r) = *reinterpret_cast<const uint4 *>(src);
+  return r;
+}
+
+template <typename T, int kVec>
+__global__ void __launch_bounds__(256) fused_drem_kernel(KParams p, int group) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rows_per_warp = 32 / group;
+  const long long tok = ((long long)blockIdx.x * 8 + warp) * rows_per_warp + lane / group;
+  const int x0 = (lane % group) * kVec;
+  const long long h = blockIdx.y, b = blockIdx.z;
   float s = 0.f;
-  for (int x = lane; x < p.head_dim; x += 32) s = fmaf(to_f32<T>(g[x]), to_f32<T>(v[x]), s);
+  if (tok < p.tokens) {
+    const T *g = reinterpret_cast<const T *>(p.d_o.ptr) + b * p.d_o.sb + h * p.d_o.sh + tok * p.d_o.st;
+    const T *v = reinterpret_cast<const T *>(p.v.ptr) + b * p.v.sb + h * p.v.sh + tok * p.v.st;
+    for (int x = x0; x < p.head_dim; x += group * kVec) {
+      const RowVec<T, kVec> gv = load_vec<T, kVec>(g + x), vv = load_vec<T, kVec>(v + x);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) p.drem_f32[row] = s + (p.d_rem != nullptr ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[row]) : 0.f);
+      for (int i = 0; i < kVec; ++i) s = fmaf(to_f32<T>(gv.e[i]), to_f32<T>(vv.e[i]), s);
+    }
+  }
+  for (int o = group >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (tok < p.tokens && x0 == 0) {
+    const long long row = (b * p.heads + h) * p.tokens + tok;
+    p.drem_f32[row] = s + (p.d_rem != nullptr ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[row]) : 0.f);
+  }
+}
+
+template <typename T, int kVec>
+__global__ void __launch_bounds__(256) fused_dv_kernel(KParams p, int group) {
+  if (p.hdr[0]) return;
+  const long long covered = p.cu != nullptr ? (long long)p.hdr[1] : p.tokens;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rows_per_warp = 32 / group;
+  const long long tok = ((long long)blockIdx.x * 8 + warp) * rows_per_warp + lane / group;
+  if (tok >= covered) return;
+  const int x0 = (lane % group) * kVec;
+  const long long h = blockIdx.y, b = blockIdx.z;
+  const T *g = reinterpret_cast<const T *>(p.d_o.ptr) + b * p.d_o.sb + h * p.d_o.sh + tok * p.d_o.st;
+  T *dv = reinterpret_cast<T *>(p.dv.ptr) + b * p.dv.sb + h * p.dv.sh + tok * p.dv.st;
+  const float rem = exp2f((float)p.log_rem[(b * p.heads + h) * p.tokens + tok]);
+  for (int x = x0; x < p.head_dim; x += group * kVec) {
+    const RowVec<T, kVec> gv = load_vec<T, kVec>(g + x);
+    RowVec<T, kVec> dvv = load_vec<T, kVec>(dv + x);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) dvv.e[i] = from_f32<T>(fmaf(rem, to_f32<T>(gv.e[i]), to_f32<T>(dvv.e[i])));
+    if (kVec == 1) dv[x] = dvv.e[0];
+    else *reinterpret_cast<uint4 *>(dv + x) = *reinterpret_cast<const uint4 *>(&dvv);
+  }
+}
+
+// 16-byte accesses need rows that start on 16-byte boundaries and hold a whole number of them.
+static bool rows_vectorizable(const TensorRef &t, int head_dim, int esize) {
+  const long long m = 16 / esize;
+  return reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0 && head_dim % m == 0 && t.sb % m == 0 && t.sh % m == 0 && t.st % m == 0;
+}
+
+template <typename T, bool kDv>
+static cudaError_t launch_fused_t(const KParams &p, cudaStream_t s) {
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const bool vec = rows_vectorizable(p.d_o, p.head_dim, sizeof(T)) &&
+                   rows_vectorizable(kDv ? p.dv : p.v, p.head_dim, sizeof(T));
+  const int per_lane = vec ? kVec : 1;
+  int group = 1;
+  while (group < 32 && group * per_lane < p.head_dim) group <<= 1;
+  const long long rows_per_block = 8 * (32 / group);
+  const dim3 grid((unsigned)((p.tokens + rows_per_block - 1) / rows_per_block), p.heads, p.batch);
+  if (kDv) {
+    if (vec) fused_dv_kernel<T, kVec><<<grid, 256, 0, s>>>(p, group);
+    else fused_dv_kernel<T, 1><<<grid, 256, 0, s>>>(p, group);
+  } else {
+    if (vec) fused_drem_kernel<T, kVec><<<grid, 256, 0, s>>>(p, group);
+    else fused_drem_kernel<T, 1><<<grid, 256, 0, s>>>(p, group);
+  }
+  return cudaGetLastError();
 }
 
 cudaError_t launch_fused_drem(const KParams &p, int dtype, cudaStream_t s) {
-  const long long rows = (long long)p.batch * p.heads * p.tokens;
-  const unsigned grid = (unsigned)((rows + 7) / 8);
-  if (dtype == SB_DTYPE_F32) fused_drem_kernel<float><<<grid, 256, 0, s>>>(p);
-  else if (dtype == SB_DTYPE_BF16) fused_drem_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
-  else fused_drem_kernel<__half><<<grid, 256, 0, s>>>(p);
-  return cudaGetLastError();
-}
-
-// ... and dv gains rem * d_out on the rows that belong to a sequence (rem = 2^log_rem, from the saved fp64 value).
-template <typename T>
-__global__ void __launch_bounds__(256) fused_dv_kernel(KParams p) {
-  if (p.hdr[0]) return;
-  const long long covered = p.cu != nullptr ? (long long)p.hdr[1] : p.tokens;
-  const long long rows = (long long)p.batch * p.heads * p.tokens;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const long long tok = row % p.tokens, bh = row / p.tokens;
-  if (tok >= covered) return;
-  const long long h = bh % p.heads, b = bh / p.heads;
-  const T *g = reinterpret_cast<const T *>(p.d_o.ptr) + b * p.d_o.sb + h * p.d_o.sh + tok * p.d_o.st;
-  T *dv = reinterpret_cast<T *>(p.dv.ptr) + b * p.dv.sb + h * p.dv.sh + tok * p.dv.st;
-  const float rem = exp2f((float)p.log_rem[row]);
-  for (int x = lane; x < p.head_dim; x += 32) dv[x] = from_f32<T>(fmaf(rem, to_f32<T>(g[x]), to_f32<T>(dv[x])));
+  if (dtype == SB_DTYPE_F32) return launch_fused_t<float, false>(p, s);
+  if (dtype == SB_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, false>(p, s);
+  return launch_fused_t<__half, false>(p, s);
 }
 
 cudaError_t launch_fused_dv(const KParams &p, int dtype, cudaStream_t s) {
-  const long long rows = (long long)p.batch * p.heads * p.tokens;
-  const unsigned grid = (unsigned)((rows + 7) / 8);
-  if (dtype == SB_DTYPE_F32) fused_dv_kernel<float><<<grid, 256, 0, s>>>(p);
-  else if (dtype == SB_DTYPE_BF16) fused_dv_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
-  else fused_dv_kernel<__half><<<grid, 256, 0, s>>>(p);
-  return cudaGetLastError();
+  if (dtype == SB_DTYPE_F32) return launch_fused_t<float, true>(p, s);
+  if (dtype == SB_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, true>(p, s);
+  return launch_fused_t<__half, true>(p, s);
 }
 
 cudaError_t launch_zero_tail(const KParams &p, int dtype, bool backward, cudaStream_t s) {
