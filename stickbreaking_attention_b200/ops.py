@@ -203,6 +203,78 @@ def _op_attn_bwd(do: torch.Tensor, dr: torch.Tensor, q: torch.Tensor, k: torch.T
     _bwd_impl(True, do, dr, q, k, v, None, None, log_rem, logit_scale, attend_current, False, dq, dk, dv)
 
 
+# ---- functional operators: what ``torch.compile`` traces ----------------------------------------
+# The mutating operators above mirror the reference's registration.  Tracing with ``fullgraph=True`` additionally
+# needs operators that allocate their own outputs, have a shape-only ("fake") implementation and carry their own
+# autograd formula, so that the tracer never has to look inside the launchers (pointer alignment checks, ctypes).
+
+@torch.library.custom_op(f"{NAMESPACE}::fwd", mutates_args=(), device_types="cuda")
+def _op_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: Optional[torch.Tensor],
+            max_seqlens: int, logit_scale: float, attend_current: bool, leading_zero: bool,
+            fuse_rem_v: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    fixed = cu_seqlens is None
+    o = torch.empty_like(q)
+    rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
+    log_rem = torch.empty(q.shape[:-1], dtype=torch.float64, device=q.device)
+    ends = None if fixed else _strip(cu_seqlens, leading_zero)
+    _fwd_impl(fixed, _tma_ready(q), _tma_ready(k), _tma_ready(v), ends, max_seqlens if max_seqlens > 0 else None,
+              logit_scale, attend_current, leading_zero and not fixed, o, rem, log_rem, fuse_rem_v=fuse_rem_v)
+    return o, rem, log_rem
+
+
+@_op_fwd.register_fake
+def _(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero, fuse_rem_v):
+    return (torch.empty_like(q), q.new_empty(q.shape[:-1]), q.new_empty(q.shape[:-1], dtype=torch.float64))
+
+
+@torch.library.custom_op(f"{NAMESPACE}::bwd", mutates_args=(), device_types="cuda")
+def _op_bwd(do: torch.Tensor, dr: Optional[torch.Tensor], q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+            cu_seqlens: Optional[torch.Tensor], max_seqlens: int, log_rem: torch.Tensor, logit_scale: float,
+            attend_current: bool, leading_zero: bool,
+            fuse_rem_v: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    fixed = cu_seqlens is None
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ends = None if fixed else _strip(cu_seqlens, leading_zero)
+    if dr is None and not fuse_rem_v:
+        dr = torch.zeros(q.shape[:-1], dtype=q.dtype, device=q.device)
+    _bwd_impl(fixed, _tma_ready(do.to(q.dtype)), None if dr is None else dr.to(q.dtype).contiguous(), _tma_ready(q),
+              _tma_ready(k), _tma_ready(v), ends, max_seqlens if max_seqlens > 0 else None, log_rem, logit_scale,
+              attend_current, leading_zero and not fixed, dq, dk, dv, fuse_rem_v=fuse_rem_v)
+    return dq, dk, dv
+
+
+@_op_bwd.register_fake
+def _(do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current, leading_zero, fuse_rem_v):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _fwd_setup_context(ctx, inputs, output):
+    q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero, fuse_rem_v = inputs
+    ctx.save_for_backward(q, k, v, output[2], cu_seqlens)
+    ctx.args = (max_seqlens, logit_scale, attend_current, leading_zero, fuse_rem_v)
+
+
+def _fwd_backward(ctx, do, drem, dlog_rem):
+    q, k, v, log_rem, cu_seqlens = ctx.saved_tensors
+    max_seqlens, logit_scale, attend_current, leading_zero, fuse_rem_v = ctx.args
+    if do is None:
+        do = torch.zeros_like(q)
+    dq, dk, dv = _op_bwd(do, drem, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current,
+                         leading_zero, fuse_rem_v)
+    return dq, dk, dv, None, None, None, None, None, None
+
+
+torch.library.register_autograd(f"{NAMESPACE}::fwd", _fwd_backward, setup_context=_fwd_setup_context)
+
+
+def functional_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, leading_zero=False,
+                   fuse_rem_v=False):
+    """``(o, rem, log_rem)`` through the functional operator ``stickbreaking_attention_b200::fwd`` (differentiable in
+    q, k, v through ``::bwd``); the public functions take this route while ``torch.compile`` is tracing."""
+    return _op_fwd(q, k, v, cu_seqlens, 0 if max_seqlens is None else int(max_seqlens), float(logit_scale),
+                   bool(attend_current), bool(leading_zero), bool(fuse_rem_v))
+
+
 def _compiling() -> bool:
     return torch.compiler.is_compiling()
 

@@ -34,6 +34,9 @@ def sb_attn(q, k, v, inv_temp=None, zero_start=True, attend_current=False):
     """``zero_start`` is accepted and ignored, as in the reference (``sb_attn/__init__.py:57``)."""
     if inv_temp is None:
         inv_temp = 1 / math.sqrt(q.size(-1))
+    if torch.compiler.is_compiling():   # one traceable operator with its own autograd formula
+        o, rem, _ = ops.functional_fwd(q, k, v, None, None, inv_temp, attend_current)
+        return o, rem
     return sb_attn_(q, k, v, inv_temp, attend_current=attend_current)
 
 
@@ -63,4 +66,6 @@ def sb_attn_fused(q, k, v, inv_temp=None, zero_start=True, attend_current=False)
     """Same arguments as ``sb_attn``; returns ``o + rem[..., None] * v`` (``tests/test_attn.py:64`` of the reference)."""
     if inv_temp is None:
         inv_temp = 1 / math.sqrt(q.size(-1))
+    if torch.compiler.is_compiling():
+        return ops.functional_fwd(q, k, v, None, None, inv_temp, attend_current, fuse_rem_v=True)[0]
     return StickBreakingAttentionFused.apply(q, k, v, inv_temp, attend_current)

@@ -48,6 +48,9 @@ def sb_attn_varlen(q, k, v, cu_seqlens, max_seqlens=None, inv_temp=None, zero_st
     """
     if inv_temp is None:
         inv_temp = 1 / math.sqrt(q.size(-1))
+    if torch.compiler.is_compiling():   # one traceable operator with its own autograd formula
+        o, rem, _ = ops.functional_fwd(q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current, bool(zero_start))
+        return o, rem
     return sb_attn_varlen_(q, k, v, inv_temp, cu_seqlens, max_seqlens, attend_current, bool(zero_start))
 
 
@@ -82,5 +85,8 @@ def sb_attn_varlen_fused(q, k, v, cu_seqlens, max_seqlens=None, inv_temp=None, z
     callers compute from its two outputs (``tests/test_varlen.py:101``), without the extra passes over o and v."""
     if inv_temp is None:
         inv_temp = 1 / math.sqrt(q.size(-1))
+    if torch.compiler.is_compiling():
+        return ops.functional_fwd(q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current, bool(zero_start),
+                                  fuse_rem_v=True)[0]
     return StickBreakingAttentionFused.apply(q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current,
                                              bool(zero_start))

@@ -163,6 +163,45 @@ def test_fused_rem_v_fixed(sb, cuda_device, shape, dtype):
     H.assert_fused_parity(got, H.oracle_fused(q, k, v, dout), dtype, "fused fixed")
 
 
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
+def test_torch_compile_fullgraph(sb, cuda_device, backend):
+    """torch.compile(fullgraph=True) traces the public functions as one functional operator each (fake implementation
+    and autograd formula registered), and the compiled step returns exactly what eager mode returns."""
+    lengths = [300, 724]
+    q, k, v, do, drem = (t.to(cuda_device) for t in H.make_inputs((4, 1024, 128), torch.bfloat16, seed=7, std=0.5))
+    cu = cu_of(lengths, True).to(cuda_device)
+    q4, k4, v4 = (t.reshape(2, 2, 1024, 128) for t in (q, k, v))
+
+    def step(q, k, v, q4, k4, v4):
+        o, rem = sb.sb_attn_varlen(q, k, v, cu, 724)
+        out = sb.sb_attn_varlen_fused(q, k, v, cu, 724)
+        o4, rem4 = sb.sb_attn(q4, k4, v4)
+        return o, rem, out, o4, rem4
+
+    def run(fn):
+        ins = [t.clone().requires_grad_(True) for t in (q, k, v, q4, k4, v4)]
+        outs = fn(*ins)
+        ups = (do, drem, do, do.reshape(2, 2, 1024, 128), drem.reshape(2, 2, 1024))
+        return outs, torch.autograd.grad(outs, ins, ups)
+
+    torch._dynamo.reset()
+    want_o, want_g = run(step)
+    got_o, got_g = run(torch.compile(step, backend=backend, fullgraph=True))
+    for a, b in zip(got_o + got_g, want_o + want_g):
+        assert torch.equal(a, b)
+
+
+def test_functional_operator_opcheck(sb, cuda_device):
+    """torch.library.opcheck: schema, fake implementation, autograd registration and AOT dispatch of the operator
+    that torch.compile sees."""
+    q, k, v, _, _ = (t.to(cuda_device) for t in H.make_inputs((2, 384, 64), torch.bfloat16, seed=9, std=0.5))
+    cu = cu_of([100, 284]).to(cuda_device)
+    args = (q.requires_grad_(), k.requires_grad_(), v.requires_grad_(), cu, 284, 0.125, False, False, False)
+    torch.library.opcheck(torch.ops.stickbreaking_attention_b200.fwd.default, args)
+    args4 = tuple(t.detach().reshape(1, 2, 384, 64).requires_grad_() for t in (q, k, v)) + (None, 0, 0.125, True, False, True)
+    torch.library.opcheck(torch.ops.stickbreaking_attention_b200.fwd.default, args4)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_varlen_forms_agree(sb, cuda_device, dtype):
     """zero_start / int32 / missing max_seqlens / empty sequences are the same computation."""

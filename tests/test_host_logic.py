@@ -122,3 +122,22 @@ def test_benchmark_sweep_host_side():
     if not torch.cuda.is_available():
         with pytest.raises(SystemExit):
             benchmarks.main(["--op", "attn", "--lengths", "256"])
+
+
+def test_functional_operator_traces_without_a_device():
+    """What torch.compile relies on: the functional operator has a shape-only implementation, so a trace with fake
+    tensors records one call of it and the right output shapes, dtypes and strides without running any kernel."""
+    from torch.fx.experimental.proxy_tensor import make_fx
+    from stickbreaking_attention_b200 import ops
+    q = torch.randn(40, 3, 16).permute(1, 0, 2)          # (heads, tokens, d) view of token-major storage
+    cu = torch.tensor([0, 15, 40])
+
+    def f(q, k, v, cu):
+        return ops.functional_fwd(q, k, v, cu, None, 0.25, leading_zero=True)
+
+    gm = make_fx(f, tracing_mode="fake")(q, q, q, cu)
+    calls = [n for n in gm.graph.nodes if n.op == "call_function" and "stickbreaking_attention_b200.fwd" in str(n.target)]
+    assert len(calls) == 1
+    o, rem, log_rem = (n.meta["val"] for n in gm.graph.find_nodes(op="output")[0].args[0])
+    assert o.shape == q.shape and o.stride() == q.stride() and o.dtype == q.dtype
+    assert rem.shape == q.shape[:-1] and log_rem.shape == q.shape[:-1] and log_rem.dtype == torch.float64
