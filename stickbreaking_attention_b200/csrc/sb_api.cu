@@ -243,7 +243,8 @@ static int run(const SbParams *p, void *stream, bool backward) {
       if (e != cudaSuccess) return fail(SB_ERR_CUDA, "tail launch: %s", cudaGetErrorString(e));
     }
   }
-  if (backward && k.fuse_rem_v && !k.skip_dkv) {
+  // the stored-tiles dK/dV kernel adds rem * d_out in its own epilogue; the other kernels leave it to one more pass
+  if (backward && k.fuse_rem_v && !k.skip_dkv && !(pl.path == SB_PATH_TCGEN05 && pl.store_az)) {
     e = launch_fused_dv(k, p->dtype, s);
     g_launches += 1;
     if (e != cudaSuccess) return fail(SB_ERR_CUDA, "dv launch: %s", cudaGetErrorString(e));

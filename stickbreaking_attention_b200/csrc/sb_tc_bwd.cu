@@ -1254,12 +1254,20 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
       tc_fence_after();
       const int key = J * kBM + r;
       const bool valid = key < c.len;
+      // out = o + rem * v was requested: dV gains rem * d_out on its own row (rem = 2^log_rem)
+      const T *grow = nullptr;
+      float rem_f = 0.f;
+      if (p.fuse_rem_v && valid) {
+        grow = reinterpret_cast<const T *>(p.d_o.ptr) + c.boff * p.d_o.sb + (long long)h * p.d_o.sh + (c.tok0 + key) * p.d_o.st;
+        rem_f = exp2f((float)p.log_rem[(c.boff * p.heads + h) * p.tokens + c.tok0 + key]);
+      }
       if (J * kBM + kBM <= c.len) {
         // full tile: through the first two stages' memory (all MMAs are done), one TMA store per warp and half
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           uint8_t *stage = gbase + which * kStageBytes;                // [128 x 128] as two blocks of 128-byte rows
-          stage_acc_rows<D, kFp16>(tmem + which * 128 + lane_off, stage, r, which == 0 ? p.scale : 1.f);
+          stage_acc_rows<D, kFp16>(tmem + which * 128 + lane_off, stage, r, which == 0 ? p.scale : 1.f,
+                                   which == 1 ? grow : nullptr, rem_f, p.head_dim);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -1277,7 +1285,7 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
         T *krow = reinterpret_cast<T *>(p.dk.ptr) + c.boff * p.dk.sb + (long long)h * p.dk.sh + (c.tok0 + key) * p.dk.st;
         T *vrow = reinterpret_cast<T *>(p.dv.ptr) + c.boff * p.dv.sb + (long long)h * p.dv.sh + (c.tok0 + key) * p.dv.st;
         store_acc_rows<D, kFp16, T>(tmem + lane_off, krow, valid, p.head_dim, p.scale);
-        store_acc_rows<D, kFp16, T>(tmem + 128 + lane_off, vrow, valid, p.head_dim, 1.f);
+        store_acc_rows<D, kFp16, T>(tmem + 128 + lane_off, vrow, valid, p.head_dim, 1.f, grow, rem_f);
       }
     }
   }
