@@ -67,3 +67,56 @@ def test_131072_sequence_sampled_rows_and_properties(sb, cuda_device, std):
     _, _, dq2, dk2, dv2 = H.run_varlen(sb, q, k, v, 2 * do, 2 * drem, cu, cuda_device, max_seqlens=L)
     for a, b in ((dq2, dq), (dk2, dk), (dv2, dv)):
         assert torch.equal(a.float(), 2 * b.float())
+
+
+def _check_sampled_sequences(sb, dev, q, k, v, do, drem, lengths, picks, *, backward, what):
+    """Runs the whole packed batch on the GPU and compares the picked sequences (each is independent of the others)
+    with the oracle run on that sequence alone."""
+    cu = torch.tensor(lengths).cumsum(0)
+    starts = [0] + cu.tolist()[:-1]
+    if backward:
+        got = H.run_varlen(sb, q, k, v, do, drem, cu, dev, max_seqlens=max(lengths))
+    else:
+        with torch.no_grad():
+            o, rem = sb.sb_attn_varlen(q.to(dev), k.to(dev), v.to(dev), cu.to(dev), max(lengths), zero_start=False)
+        got = (o.cpu(), rem.cpu())
+    for t in got:
+        assert torch.isfinite(t.float()).all()
+    assert torch.all(got[0][:, starts] == 0) and torch.all(got[1][:, starts] == 1)
+    for s in picks:
+        a, b = starts[s], starts[s] + lengths[s]
+        one = torch.tensor([lengths[s]])
+        want = H.oracle_varlen(q[:, a:b], k[:, a:b], v[:, a:b], do[:, a:b], drem[:, a:b], one)
+        mine = [t[:, a:b] for t in got]
+        if backward:
+            H.assert_parity(mine, want, q.dtype, f"{what} sequence {s}")
+        else:
+            for name, x, y in zip(("o", "rem"), mine, want[:2]):
+                assert H.max_abs(x, y) <= H.TOL[q.dtype]["out"], f"{what} sequence {s}: {name}"
+    return got
+
+
+def test_many_short_sequences_forward_shape_of_the_serving_configuration(sb, cuda_device):
+    """4096 sequences of 128..512 tokens, head_dim 64, forward only (two of the 32 heads): about 1.3 M tokens, more
+    work items than fit the forward's persistent grid many times over.  Sampled sequences against the oracle."""
+    gen = torch.Generator().manual_seed(55)
+    lengths = torch.randint(128, 513, (4096,), generator=gen).tolist()
+    q, k, v, do, drem = H.make_inputs((2, sum(lengths), 64), torch.bfloat16, seed=56, std=0.5)
+    picks = [0, 1, 777, 2048, 4094, 4095, lengths.index(max(lengths)), lengths.index(min(lengths))]
+    _check_sampled_sequences(sb, cuda_device, q, k, v, do, drem, lengths, picks, backward=False, what="short")
+
+
+def test_lognormal_lengths_training_configuration(sb, cuda_device):
+    """65536 tokens cut into sequences of lognormal length (median 1024, clipped to 64..16384), head_dim 128, forward
+    and backward (two of the 32 heads): the uneven mix the weight-ordered schedule is built for.  Sampled sequences,
+    the longest and the shortest among them, against the oracle."""
+    gen = torch.Generator().manual_seed(3)
+    lengths, total = [], 65536
+    while sum(lengths) < total:
+        n = int(torch.exp(torch.randn((), generator=gen) + 6.931).clamp(64, 16384))
+        lengths.append(min(n, total - sum(lengths)))
+    q, k, v, do, drem = H.make_inputs((2, total, 128), torch.bfloat16, seed=57, std=0.5)
+    order = sorted(range(len(lengths)), key=lambda i: lengths[i])
+    picks = sorted({order[0], order[len(order) // 2], order[-1], 0, len(lengths) - 1})
+    picks = [s for s in picks if lengths[s] <= 8192] or [order[0]]
+    _check_sampled_sequences(sb, cuda_device, q, k, v, do, drem, lengths, picks, backward=True, what="lognormal")
