@@ -62,7 +62,8 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   if (p->struct_bytes != (int)sizeof(SbParams))
     return fail(SB_ERR_ARGUMENT, "struct_bytes %d != sizeof(SbParams) %d", p->struct_bytes, (int)sizeof(SbParams));
   if (p->dtype < SB_DTYPE_F32 || p->dtype > SB_DTYPE_F16) return fail(SB_ERR_ARGUMENT, "unknown dtype %d", p->dtype);
-  if (p->batch < 1 || p->heads < 1 || p->heads > 65535) return fail(SB_ERR_ARGUMENT, "batch/heads out of range");
+  if (p->batch < 1 || p->batch > 65535 || p->heads < 1 || p->heads > 65535)
+    return fail(SB_ERR_ARGUMENT, "batch/heads out of range (1..65535)");
   if (p->head_dim < 1 || p->head_dim > 256) return fail(SB_ERR_ARGUMENT, "head_dim %d outside 1..256", p->head_dim);
   if (p->tokens < 0 || p->tokens > 0x7fffff00LL) return fail(SB_ERR_ARGUMENT, "tokens out of range");
   if (p->cu_seqlens != nullptr) {
