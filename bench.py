@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the stick-breaking attention hot path: sb_attn_varlen forward + backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2s|c3|c4|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2s|c3|c4|c5|c5s]
 
 One step = one forward + backward pass of ``sb_attn_varlen`` over one synthetic batch.  The default
 workload is the configuration the headline metric is quoted on: 16 heads, head_dim 128, 8 sequences of
@@ -71,6 +71,11 @@ def workload(name: str, seed: int = 0):
     if name == "c4":
         return dict(heads=16, head_dim=128, lengths=[131072], std=0.5, zero_start=False, fwd_only=False,
                     label="16 heads x 1 sequence of 131072 tokens, head_dim 128, bf16, fwd+bwd")
+    if name == "c5s":     # small stand-in of c5 used for profiler captures
+        rng = np.random.default_rng(seed)
+        lengths = rng.integers(128, 513, size=1024).tolist()
+        return dict(heads=8, head_dim=64, lengths=lengths, std=1.0, zero_start=False, fwd_only=True,
+                    label="8 heads, 1024 sequences of 128..512 tokens, head_dim 64, bf16, forward only")
     if name == "c5":
         rng = np.random.default_rng(seed)
         lengths = rng.integers(128, 513, size=4096).tolist()
@@ -392,6 +397,16 @@ def run_gpu_arm(args, w):
                     "peak_source": f"{peak_kind} dense bf16 (burst)", "kernels": kernels,
                     "step_frac_of_peak": value / world / peaks["bf16_tflops"],
                     "kernel_path": "tcgen05" if path == 1 else "cuda-core"}
+        if fwd_only:
+            # forward-only workloads with a low arithmetic intensity sit under the HBM roof: q, k, v read once, o, rem
+            # and log_rem written once are the algorithmic bytes
+            tokens, esz = sum(w["lengths"]), 2
+            alg_bytes = w["heads"] * tokens * (4 * w["head_dim"] * esz + esz + 8)
+            if fl / alg_bytes < peaks["bf16_tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9):
+                gbs = alg_bytes / (kern["fwd"] * 1e-3) / 1e9
+                roofline.update({"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": gbs / peaks["hbm_gbs"], "peak_source": f"{peak_kind} HBM copy",
+                                 "algorithmic_bytes": alg_bytes})
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             heads = min(8, w["heads"])
