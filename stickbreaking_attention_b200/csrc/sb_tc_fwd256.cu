@@ -280,7 +280,9 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int ac = p.attend_current;
     int U = 0;
     bool ok = true;
-    for (int it = 0; ok && fwd256_item(p, it, w); ++it) {
+    Fwd256Item w_next;
+    bool have = fwd256_item(p, 0, w);
+    for (int it = 0; ok && have; ++it) {
       const bool active = wg == 0 || w.b_active;
       const int t0 = wg == 0 ? w.t0_a : 0;
       const int my_steps = active ? w.n_steps - t0 : 0;
@@ -315,13 +317,20 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       // ---- epilogue: O (TMEM) -> global, rem, log_rem
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 42 + wg, it);
+      // While the last P V MMA finishes: rem and log_rem leave, and the next item's table entries are fetched.
+      const bool valid = row < w.c.len;
+      const float rem_f = ex2(-(float)run);
+      if (ok && my_steps > 0 && valid) {
+        const long long idx = (w.c.boff * p.heads + w.h) * p.tokens + w.c.tok0 + row;
+        reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(rem_f);
+        p.log_rem[idx] = -run;
+      }
+      const bool have_next = fwd256_item(p, it + 1, w_next);
       if (ok) ok = wait_or_abort(bar(bOFull + wg), it & 1, abort_flag, p, 332);
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 44 + wg, it);
       if (ok && my_steps > 0) {
         tc_fence_after();
-        const bool valid = row < w.c.len;
         const int tile_row0 = w.blk_row0 + wg * kBM;
-        const float rem_f = ex2(-(float)run);
         // out = o + rem * v on request: this row of V comes straight from global memory
         const T *vrow = (p.fuse_rem_v && valid) ? reinterpret_cast<const T *>(p.v.ptr) + w.c.boff * p.v.sb +
                                                       (long long)w.h * p.v.sh + (w.c.tok0 + row) * p.v.st
@@ -343,17 +352,14 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           T *orow = reinterpret_cast<T *>(p.o.ptr) + w.c.boff * p.o.sb + (long long)w.h * p.o.sh + (w.c.tok0 + row) * p.o.st;
           store_acc_rows<D, kFp16, T>(tmem + 256 + wg * 128 + lane_off, orow, valid, p.head_dim, 1.f, vrow, rem_f);
         }
-        if (valid) {
-          const long long idx = (w.c.boff * p.heads + w.h) * p.tokens + w.c.tok0 + row;
-          reinterpret_cast<T *>(p.rem)[idx] = from_f32<T>(rem_f);
-          p.log_rem[idx] = -run;
-        }
       }
       tc_fence_before();            // the accumulator has been read: the next item may overwrite it
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(bOFree + wg));
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 46 + wg, it);
       U += my_steps;
+      w = w_next;
+      have = have_next;
     }
     if (lane == 0) tma_store_wait_all();
   }
