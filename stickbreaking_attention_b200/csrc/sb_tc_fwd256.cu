@@ -17,7 +17,7 @@ namespace sb {
 namespace fwd256 {
 constexpr int kThreads = 352;
 constexpr int kBN = 64;                       // keys per sub-tile
-constexpr int kStages = 3;
+constexpr int kMaxStages = 6;
 constexpr int kKvBoxBytes = kBN * 64 * 2;     // one 64-row x 64-column box
 constexpr int kPBytes = kBM * kBN * 2;        // one P buffer: 128 rows x 64 keys
 constexpr int kBarBytes = 512;
@@ -27,9 +27,14 @@ struct Cfg {
   static constexpr int kQBytes = kBM * D * 2;                  // one 128-row Q tile
   static constexpr int kKvTileBytes = kBoxes * kKvBoxBytes;    // K or V sub-tile: 64 keys x D columns
   static constexpr int kStageBytes = 2 * kKvTileBytes;         // K and V
+  // K/V ring: three stages at 128 columns fill the shared memory; at 64 columns six fit, and short sequences need
+  // them: a stage is reloaded only after both tiles' P V MMAs of its step, so with three stages the load for step
+  // s + 3 starts one row pass before its scores are wanted, which the ~2000 clk load latency does not always meet
+  static constexpr int kStages = D == 64 ? 6 : 3;
   static constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
 };
-enum { bQ = 0, bKvFull = 1, bKvEmpty = 4, bSFull = 7, bQFree = 11, bOFree = 12, bPFull = 15, bPEmpty = 19, bOFull = 23, bNum = 25 };
+enum { bQ = 0, bKvFull = 1, bKvEmpty = 7, bSFull = 13, bQFree = 17, bOFree = 18, bPFull = 20, bPEmpty = 24, bOFull = 28, bNum = 30 };
+static_assert(bKvEmpty - bKvFull == kMaxStages && bSFull - bKvEmpty == kMaxStages, "barrier slots per stage");
 // per-warpgroup barrier index: base + wg * 2 + buf
 }  // namespace fwd256
 
@@ -135,6 +140,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   using namespace fwd256;
   using C = Cfg<D>;
   constexpr int kQBytes = C::kQBytes, kKvTileBytes = C::kKvTileBytes, kStageBytes = C::kStageBytes, kBoxes = C::kBoxes;
+  constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
