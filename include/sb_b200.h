@@ -65,7 +65,7 @@ enum SbFlags {
   SB_FLAG_BWD_SKIP_DKV = 4, /* timing aid: sb_bwd enqueues only the dQ kernel                   */
   SB_FLAG_BWD_SKIP_DQ = 8,  /* timing aid: sb_bwd enqueues only the dK/dV kernel, which then reads
                             what a previous full sb_bwd left in the same workspace              */
-  SB_FLAG_BWD_RECOMPUTE = 16, /* small-workspace backward.  By default (16-bit tensors, head_dim 72..128)
+  SB_FLAG_BWD_RECOMPUTE = 16, /* small-workspace backward.  By default (16-bit tensors, head_dim up to 128)
                             the dQ kernel stores its A and dz tiles -- 64 KiB per (query tile, key tile)
                             pair and head, heads processed in chunks of at most 8 GiB -- and the dK/dV
                             kernel is two plain GEMMs over them.  With this flag, or when one head
@@ -99,7 +99,8 @@ typedef struct SbParams {
   int32_t cu_seqlens_int64; /* element type of cu_seqlens: 0 = int32, 1 = int64                 */
   float logit_scale;    /* multiplies <q,k>; the reference default is 1/sqrt(head_dim)          */
   int32_t flags;        /* SbFlags                                                              */
-  int32_t reserved;     /* 0.  Diagnostics: 0x100 makes sb_workspace_bytes() 128 KiB larger; in a library built  *
+  int32_t reserved;     /* 0.  Low byte 64 with head_dim <= 64: sb_bwd runs the earlier one-tile kernels (kept  *
+                         * for comparison runs).  Diagnostics: 0x100 makes sb_workspace_bytes() 128 KiB larger; in a library built  *
                          * with -DSB_TRACE, block (0,0) of the tensor-core kernels logs (event, SM clock)   *
                          * pairs per role into that tail                                                    */
   const void *cu_seqlens; /* device, num_seq sequence END offsets, or NULL                      */

@@ -815,7 +815,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t src = sZ + w * kZBytes + (warp & 3) * 32 * 128;
         const int trow = (int)c.tok0 + I * kBM + (warp & 3) * 32;
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < (p.head_dim > 64 ? 2 : 1); ++half) {   // columns past head_dim do not exist
 #pragma unroll 1
           for (int ch = 0; ch < 2; ++ch) {
             uint32_t v[32];
@@ -1119,7 +1119,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (r == 0 && (ok = wait_or_abort(bar(bStaged + w), round & 1, abort_flag, p, 633))) {
             const int krow = (int)c.tok0 + J * kBM + hf * kBN;
             tma_store_4d(omap, stage_addr, 0, krow, h, (int)c.boff);
-            tma_store_4d(omap, stage_addr + kBN * 128, 64, krow, h, (int)c.boff);
+            if (p.head_dim > 64) tma_store_4d(omap, stage_addr + kBN * 128, 64, krow, h, (int)c.boff);
             tma_store_commit();
             tma_store_wait_read();
             mbar_arrive(bar(bDrained + w));
@@ -1275,7 +1275,7 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
             const int trow = (int)c.tok0 + J * kBM + warp * 32;
             const CUtensorMap *omap = which == 0 ? &tm_dk : &tm_dv;
             tma_store_4d(omap, src, 0, trow, h, (int)c.boff);
-            tma_store_4d(omap, src + kBoxBytes, 64, trow, h, (int)c.boff);
+            if (p.head_dim > 64) tma_store_4d(omap, src + kBoxBytes, 64, trow, h, (int)c.boff);
             tma_store_commit();
           }
         }
@@ -1361,7 +1361,10 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
 cudaError_t launch_tc_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches) {
   *launches += (p.skip_dq ? 0 : 1) + (p.skip_dkv ? 0 : 1);
   const bool f16 = dtype == SB_DTYPE_F16;
-  if (p.head_dim <= 64) return f16 ? launch_bwd_t<64, true>(p, dtype, s) : launch_bwd_t<64, false>(p, dtype, s);
+  // Head sizes up to 64 run the 128-column kernels too: TMA fills the missing columns with zeros, and the row passes,
+  // which bound these kernels, do not depend on the head size (the 64-column kernels above are the earlier design:
+  // one tile per block, no stored tiles; measured 20 % slower).
+  if (p.head_dim <= 64 && p.dbg == 64) return f16 ? launch_bwd_t<64, true>(p, dtype, s) : launch_bwd_t<64, false>(p, dtype, s);
   return f16 ? launch_bwd_t<128, true>(p, dtype, s) : launch_bwd_t<128, false>(p, dtype, s);
 }
 

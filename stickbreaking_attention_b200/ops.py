@@ -45,7 +45,7 @@ def force_simt(enabled: bool = True):
 def small_backward_workspace(enabled: bool = True):
     """Within the block the backward keeps its workspace small: the dK/dV kernel recomputes the attention tiles from
     boundary values (a few KiB per tile pair) instead of reading the 64 KiB per pair the dQ kernel would store for it
-    (``SB_FLAG_BWD_RECOMPUTE``).  Slower at head sizes 72..128, same results to rounding."""
+    (``SB_FLAG_BWD_RECOMPUTE``).  Slower, same results to rounding."""
     old = _state["bwd_recompute"]
     _state["bwd_recompute"] = enabled
     try:
