@@ -99,8 +99,7 @@ typedef struct SbParams {
   int32_t cu_seqlens_int64; /* element type of cu_seqlens: 0 = int32, 1 = int64                 */
   float logit_scale;    /* multiplies <q,k>; the reference default is 1/sqrt(head_dim)          */
   int32_t flags;        /* SbFlags                                                              */
-  int32_t reserved;     /* 0.  Low byte 64 with head_dim <= 64: sb_bwd runs the earlier one-tile kernels (kept  *
-                         * for comparison runs).  Diagnostics: 0x100 makes sb_workspace_bytes() 128 KiB larger; in a library built  *
+  int32_t reserved;     /* 0.  Diagnostics: 0x100 makes sb_workspace_bytes() 128 KiB larger; in a library built  *
                          * with -DSB_TRACE, block (0,0) of the tensor-core kernels logs (event, SM clock)   *
                          * pairs per role into that tail                                                    */
   const void *cu_seqlens; /* device, num_seq sequence END offsets, or NULL                      */

@@ -108,8 +108,7 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   // Stored-tiles mode (128-column head sizes): 64 KiB per (query tile, key tile) pair and head.  Taken when at least one
   // head fits the budget and the caller did not ask for the small-workspace mode.
   pl.az_bytes_per_head = (size_t)pl.pairs_cap * 2 * kTcTile * kTcTile * 2;
-  const bool first_design = p->head_dim <= 64 && (p->reserved & 0xff) == 64;   // comparison runs: the one-tile kernels
-  pl.store_az = backward && tc && !first_design && !(p->flags & SB_FLAG_BWD_RECOMPUTE) &&
+  pl.store_az = backward && tc && !(p->flags & SB_FLAG_BWD_RECOMPUTE) &&
                 pl.az_bytes_per_head <= kBoundaryBudget;
   const size_t per_head = pl.store_az ? pl.az_bytes_per_head : 2 * pl.bnd_bytes_per_head;
   size_t chunk = per_head ? kBoundaryBudget / per_head : (size_t)p->heads;

@@ -1,15 +1,17 @@
 // Tensor-core backward kernels for bf16 / fp16 tensors (reference counterpart: _backward_one_row,
 // sb_varlen_bwd.py:297-481, which accumulates dK/dV across blocks under a global spin lock).
 //
-// Two kernels, no atomics, no locks, fixed summation order:
-//   dq kernel   query-stationary.  Walks the key tiles 0 -> diagonal; per tile S = Q K^T and dP = dO V^T go to
-//               TMEM, one thread per query row recomputes A and dz = G - beta * C with the log-space suffix sum
-//               (fp64 across tiles, started from the saved log_rem) and the prefix sum C of G carried in
-//               registers, writes dz as a 16-bit tile, and dQ += dz K accumulates in TMEM.  It also records,
-//               per (row, key tile), the two carried values at the tile start (R1, S2).
-//   dkv kernel  key-stationary.  For its key tile it walks the query tiles diagonal -> end, restarts the row
-//               pass of each tile from the recorded R1/S2, and accumulates dK += dz^T Q and dV += A^T dO in TMEM.
-// Roles per CTA as in the forward kernel: warps 0-3 rows, warp 4 TMA, warp 5 MMA issue.  All waits are bounded.
+// Two kernels per call, no atomics, no locks, fixed summation order:
+//   dq kernel (tc_bwd_dq2_kernel)   query-stationary, 256 query rows per block.  Walks the keys 0 -> diagonal in
+//               64-key sub-tiles; per step S = Q K^T and dP = dO V^T go to TMEM, one thread per query row recomputes
+//               A and dz = G - beta * C with the log-space suffix sum (fp64 across tiles, started from the saved
+//               log_rem) and the prefix sum C of G carried in registers, writes dz as a 16-bit tile, and
+//               dQ += dz K accumulates in TMEM.  It leaves for the second kernel either its A and dz tiles
+//               (stored-tiles mode) or, every 32 keys, the two carried values R1 and S2 (small-workspace mode).
+//   dK/dV kernel  key-stationary, one 128-key tile per block, query tiles diagonal -> end.
+//               tc_bwd_dkv5_kernel: dK += dz^T Q and dV += A^T dO as plain GEMMs over the stored tiles.
+//               tc_bwd_dkv4_kernel: repeats the row pass of each tile from the recorded R1/S2 first.
+// Head sizes below 128 run the same code: TMA zero-fills the columns past head_dim.  All waits are bounded.
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -122,384 +124,6 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uin
   bwd_row_chunk_values<kMasked>(s, dp, mc0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
   if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
   store_row_chunk16<kFp16>(tile_z, r, c0, pz);
-}
-
-// One row of a 128-key tile.  `empty_bar` is signalled (one arrival per warp) as soon as the last columns of S and
-// dP are in registers.  TMEM is read one 16-column load ahead of the arithmetic.  mid_r1 / mid_s2 (optional)
-// receive the carried values at key 64 of the tile.
-template <bool kFp16, bool kStoreA, bool kMasked>
-__device__ __forceinline__ void bwd_row_pass(uint32_t ts, uint32_t tp, uint32_t empty_bar, int lane, int r, bool diag,
-                                             int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
-                                             float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z, float *mid_r1,
-                                             float *mid_s2) {
-  uint32_t s0[16], d0[16], s1[16], d1[16];
-  tmem_ld16(ts, s0);
-  tmem_ld16(tp, d0);
-#pragma unroll 1
-  for (int pair = 0; pair < 4; ++pair) {
-    const int c0 = pair * 32;
-    tmem_wait_ld_regs(s0, d0);
-    tmem_ld16(ts + c0 + 16, s1);
-    tmem_ld16(tp + c0 + 16, d1);
-    bwd_row_chunk<kFp16, kStoreA, kMasked>(s0, d0, c0, c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, tile_a,
-                                           tile_z);
-    tmem_wait_ld_regs(s1, d1);
-    if (pair < 3) {
-      tmem_ld16(ts + c0 + 32, s0);
-      tmem_ld16(tp + c0 + 32, d0);
-    } else {
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar);
-    }
-    bwd_row_chunk<kFp16, kStoreA, kMasked>(s1, d1, c0 + 16, c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum,
-                                           tile_a, tile_z);
-    if (pair == 1 && mid_r1 != nullptr) {
-      *mid_r1 = r1 + logsum;
-      *mid_s2 = gpre + gs;
-    }
-  }
-}
-
-// =======================================================================================================
-// dq kernel
-// =======================================================================================================
-template <int D>
-struct DqCfg {
-  static constexpr int kStages = D == 128 ? 2 : 3;
-  static constexpr int kTileBytes = kBM * D * 2;
-  static constexpr int kZBytes = kBM * kBM * 2;
-  static constexpr int kSmem = 1024 + kTileBytes * (2 + 2 * kStages) + kZBytes + 256;
-};
-enum { qQG = 0, qKvFull = 1, qKvEmpty = 4, qSpFull = 7, qSpEmpty = 8, qZFull = 9, qZEmpty = 10, qDqFull = 11, qNumBars = 12 };
-
-template <int D, bool kFp16>
-__global__ void __launch_bounds__(kTcThreads, 1)
-tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
-  using Cfg = DqCfg<D>;
-  constexpr int NS = Cfg::kStages;
-  extern __shared__ uint8_t smem_raw[];
-  if (p.hdr[0]) return;
-  TileCoord c;
-  int hh_blk;
-  if (!decode_block(p, 1, true, c, hh_blk)) return;
-
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t *gbase = smem_raw + (base - raw);
-  const uint32_t sQ = base;
-  const uint32_t sG = sQ + Cfg::kTileBytes;
-  const uint32_t sK = sG + Cfg::kTileBytes;
-  const uint32_t sV = sK + NS * Cfg::kTileBytes;
-  const uint32_t sZ = sV + NS * Cfg::kTileBytes;
-  const uint32_t sBar = sZ + Cfg::kZBytes;
-  uint8_t *gZ = gbase + (sZ - base);
-  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + qNumBars * 8);
-  volatile int *abort_flag = &ctl->abort;
-  auto bar = [&](int i) { return sBar + 8u * i; };
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = hh_blk, h = p.head0 + hh;
-  const int I = c.idx;
-  const int n_tiles = I + 1;
-  const int row0 = (int)c.tok0 + I * kBM;
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar(qQG), 1);
-    for (int s = 0; s < NS; ++s) { mbar_init(bar(qKvFull + s), 1); mbar_init(bar(qKvEmpty + s), 1); }
-    mbar_init(bar(qSpFull), 1);
-    mbar_init(bar(qSpEmpty), 4);
-    mbar_init(bar(qZFull), 4);
-    mbar_init(bar(qZEmpty), 1);
-    mbar_init(bar(qDqFull), 1);
-    ctl->abort = 0;
-    fence_barrier_init();
-  }
-  if (warp == 5) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tS = tmem, tP = tmem + 128, tDQ = tmem + 256;
-
-  if (warp == 4) {
-    if (lane == 0) {
-      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
-      mbar_arrive_expect_tx(bar(qQG), 2 * Cfg::kTileBytes);
-      for (int kb = 0; kb < D / 64; ++kb) {
-        tma_load_4d(sQ + kb * kBoxBytes, &tm_q, bar(qQG), kb * 64, row0, h, (int)c.boff);
-        tma_load_4d(sG + kb * kBoxBytes, &tm_g, bar(qQG), kb * 64, row0, h, (int)c.boff);
-      }
-      for (int j = 0; j < n_tiles; ++j) {
-        const int st = j % NS;
-        if (j >= NS && !wait_or_abort(bar(qKvEmpty + st), ((j / NS) - 1) & 1, abort_flag, p, 110)) break;
-        if (*abort_flag) break;
-        const int krow = (int)c.tok0 + j * kBM;
-        mbar_arrive_expect_tx(bar(qKvFull + st), 2 * Cfg::kTileBytes);
-        for (int kb = 0; kb < D / 64; ++kb) {
-          tma_load_4d(sK + st * Cfg::kTileBytes + kb * kBoxBytes, &tm_k, bar(qKvFull + st), kb * 64, krow, h, (int)c.boff);
-          tma_load_4d(sV + st * Cfg::kTileBytes + kb * kBoxBytes, &tm_v, bar(qKvFull + st), kb * 64, krow, h, (int)c.boff);
-        }
-      }
-    }
-  } else if (warp == 5) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_f16(kBM, kBM, kFp16, false, false);
-      constexpr uint32_t idesc_dq = idesc_f16(kBM, D, kFp16, false, true);
-      auto issue_sp = [&](int j) {   // S = Q K_j^T,  dP = dO V_j^T
-        mma_kmajor_kmajor<D>(tS, sQ, sK + (j % NS) * Cfg::kTileBytes, idesc_s, false);
-        mma_kmajor_kmajor<D>(tP, sG, sV + (j % NS) * Cfg::kTileBytes, idesc_s, false);
-        mma_commit(bar(qSpFull));
-      };
-      bool ok = wait_or_abort(bar(qQG), 0, abort_flag, p, 120) && wait_or_abort(bar(qKvFull), 0, abort_flag, p, 121);
-      if (ok) {
-        tc_fence_after();
-        issue_sp(0);
-      }
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) {
-          const int jn = j + 1;
-          ok = wait_or_abort(bar(qKvFull + jn % NS), (jn / NS) & 1, abort_flag, p, 122) &&
-               wait_or_abort(bar(qSpEmpty), j & 1, abort_flag, p, 123);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sp(jn);
-        }
-        ok = wait_or_abort(bar(qZFull), j & 1, abort_flag, p, 124);
-        if (!ok) break;
-        tc_fence_after();
-        mma_kmajor_mnmajor(tDQ, sZ, sK + (j % NS) * Cfg::kTileBytes, idesc_dq, j > 0);   // dQ += dz K_j
-        mma_commit(bar(qKvEmpty + j % NS));
-        mma_commit(bar(qZEmpty));
-      }
-      if (ok) mma_commit(bar(qDqFull));
-    }
-  } else {
-    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
-    const int r = threadIdx.x;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    const float scale2 = p.scale * kLog2e;
-    const int gi = I * kBM + r;
-    const bool valid = gi < c.len;
-    const long long idx = (c.boff * p.heads + h) * p.tokens + c.tok0 + gi;
-    double r1 = valid ? p.log_rem[idx] : 0.0;   // sum of log2(1-beta) over the keys from the current tile on
-    const float dr = valid ? load_drem<T>(p, idx) : 0.f;
-    float gpre = 0.f;
-    // boundary records: [pair][half: keys 0.. / keys 64..][row]
-    const long long slot0 = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2) * (4 * kBM) + r;
-    bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = wait_or_abort(bar(qSpFull), j & 1, abort_flag, p, 130);
-      if (ok && j > 0) ok = wait_or_abort(bar(qZEmpty), (j - 1) & 1, abort_flag, p, 131);
-      if (!ok) break;
-      tc_fence_after();
-      const float r1f = (float)r1;
-      float *rec_r1 = p.bnd_r1 + slot0 + (long long)j * (4 * kBM);
-      float *rec_s2 = p.bnd_s2 + slot0 + (long long)j * (4 * kBM);
-      rec_r1[0] = r1f;
-      rec_s2[0] = gpre;
-      float gs = 0.f, logsum = 0.f;
-      if (j == I)
-        bwd_row_pass<kFp16, false, true>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, true, p.attend_current, true,
-                                         scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ, rec_r1 + 2 * kBM, rec_s2 + 2 * kBM);
-      else
-        bwd_row_pass<kFp16, false, false>(tS + lane_off, tP + lane_off, bar(qSpEmpty), lane, r, false, 0, true, scale2, r1f, gpre,
-                                          dr, gs, logsum, nullptr, gZ, rec_r1 + 2 * kBM, rec_s2 + 2 * kBM);
-      r1 += (double)logsum;
-      gpre += gs;
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(qZFull));
-    }
-    if (ok) ok = wait_or_abort(bar(qDqFull), 0, abort_flag, p, 132);
-    if (ok) {
-      tc_fence_after();
-      T *grow = reinterpret_cast<T *>(p.dq.ptr) + c.boff * p.dq.sb + (long long)h * p.dq.sh + (c.tok0 + gi) * p.dq.st;
-      store_acc_rows<D, kFp16, T>(tDQ + lane_off, grow, valid, p.head_dim, p.scale);
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
-}
-
-// =======================================================================================================
-// dkv kernel
-// =======================================================================================================
-template <int D>
-struct DkvCfg {
-  static constexpr int kStages = D == 128 ? 1 : 2;
-  static constexpr int kTileBytes = kBM * D * 2;
-  static constexpr int kAzBytes = kBM * kBM * 2;
-  static constexpr int kSmem = 1024 + kTileBytes * (2 + 2 * kStages) + 2 * kAzBytes + 256;
-};
-enum { vKV = 0, vQgFull = 1, vQgEmpty = 3, vSpFull = 5, vSpEmpty = 6, vAzFull = 7, vAzEmpty = 8, vOutFull = 9, vNumBars = 10 };
-
-template <int D, bool kFp16>
-__global__ void __launch_bounds__(kTcThreads, 1)
-tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g, const KParams p) {
-  using Cfg = DkvCfg<D>;
-  constexpr int NS = Cfg::kStages;
-  extern __shared__ uint8_t smem_raw[];
-  if (p.hdr[0]) return;
-  TileCoord c;
-  int hh_blk;
-  if (!decode_block(p, 1, false, c, hh_blk)) return;
-
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t *gbase = smem_raw + (base - raw);
-  const uint32_t sK = base;
-  const uint32_t sV = sK + Cfg::kTileBytes;
-  const uint32_t sQ = sV + Cfg::kTileBytes;
-  const uint32_t sG = sQ + NS * Cfg::kTileBytes;
-  const uint32_t sA = sG + NS * Cfg::kTileBytes;
-  const uint32_t sZ = sA + Cfg::kAzBytes;
-  const uint32_t sBar = sZ + Cfg::kAzBytes;
-  uint8_t *gA = gbase + (sA - base);
-  uint8_t *gZ = gbase + (sZ - base);
-  Ctl *ctl = reinterpret_cast<Ctl *>(gbase + (sBar - base) + vNumBars * 8);
-  volatile int *abort_flag = &ctl->abort;
-  auto bar = [&](int i) { return sBar + 8u * i; };
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = hh_blk, h = p.head0 + hh;
-  const int J = c.idx;
-  const int cnt = c.n_tiles - J;             // query tiles J .. n_tiles-1
-  const int krow = (int)c.tok0 + J * kBM;
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar(vKV), 1);
-    for (int s = 0; s < NS; ++s) { mbar_init(bar(vQgFull + s), 1); mbar_init(bar(vQgEmpty + s), 1); }
-    mbar_init(bar(vSpFull), 1);
-    mbar_init(bar(vSpEmpty), 4);
-    mbar_init(bar(vAzFull), 4);
-    mbar_init(bar(vAzEmpty), 1);
-    mbar_init(bar(vOutFull), 1);
-    ctl->abort = 0;
-    fence_barrier_init();
-  }
-  if (warp == 5) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tS = tmem, tP = tmem + 128, tDK = tmem + 256, tDV = tmem + 256 + D;
-
-  if (warp == 4) {
-    if (lane == 0) {
-      prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_g);
-      mbar_arrive_expect_tx(bar(vKV), 2 * Cfg::kTileBytes);
-      for (int kb = 0; kb < D / 64; ++kb) {
-        tma_load_4d(sK + kb * kBoxBytes, &tm_k, bar(vKV), kb * 64, krow, h, (int)c.boff);
-        tma_load_4d(sV + kb * kBoxBytes, &tm_v, bar(vKV), kb * 64, krow, h, (int)c.boff);
-      }
-      for (int i = 0; i < cnt; ++i) {
-        const int st = i % NS;
-        if (i >= NS && !wait_or_abort(bar(vQgEmpty + st), ((i / NS) - 1) & 1, abort_flag, p, 210)) break;
-        if (*abort_flag) break;
-        const int qrow = (int)c.tok0 + (J + i) * kBM;
-        mbar_arrive_expect_tx(bar(vQgFull + st), 2 * Cfg::kTileBytes);
-        for (int kb = 0; kb < D / 64; ++kb) {
-          tma_load_4d(sQ + st * Cfg::kTileBytes + kb * kBoxBytes, &tm_q, bar(vQgFull + st), kb * 64, qrow, h, (int)c.boff);
-          tma_load_4d(sG + st * Cfg::kTileBytes + kb * kBoxBytes, &tm_g, bar(vQgFull + st), kb * 64, qrow, h, (int)c.boff);
-        }
-      }
-    }
-  } else if (warp == 5) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_f16(kBM, kBM, kFp16, false, false);
-      constexpr uint32_t idesc_kv = idesc_f16(kBM, D, kFp16, true, true);
-      auto issue_sp = [&](int i) {   // S = Q_i K^T,  dP = dO_i V^T
-        mma_kmajor_kmajor<D>(tS, sQ + (i % NS) * Cfg::kTileBytes, sK, idesc_s, false);
-        mma_kmajor_kmajor<D>(tP, sG + (i % NS) * Cfg::kTileBytes, sV, idesc_s, false);
-        mma_commit(bar(vSpFull));
-      };
-      bool ok = wait_or_abort(bar(vKV), 0, abort_flag, p, 220) && wait_or_abort(bar(vQgFull), 0, abort_flag, p, 221);
-      if (ok) {
-        tc_fence_after();
-        issue_sp(0);
-      }
-      for (int i = 0; ok && i < cnt; ++i) {
-        const int in = i + 1;
-        if (NS > 1 && in < cnt) {       // the next tile's S and dP start while this tile's rows are being finished
-          ok = wait_or_abort(bar(vQgFull + in % NS), (in / NS) & 1, abort_flag, p, 222) &&
-               wait_or_abort(bar(vSpEmpty), i & 1, abort_flag, p, 223);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sp(in);
-        }
-        ok = wait_or_abort(bar(vAzFull), i & 1, abort_flag, p, 224);
-        if (!ok) break;
-        tc_fence_after();
-        mma_mnmajor_mnmajor(tDK, sZ, sQ + (i % NS) * Cfg::kTileBytes, idesc_kv, i > 0);   // dK += dz^T Q_i
-        mma_mnmajor_mnmajor(tDV, sA, sG + (i % NS) * Cfg::kTileBytes, idesc_kv, i > 0);   // dV += A^T dO_i
-        mma_commit(bar(vQgEmpty + i % NS));
-        mma_commit(bar(vAzEmpty));
-        if (NS == 1 && in < cnt) {
-          ok = wait_or_abort(bar(vQgFull), in & 1, abort_flag, p, 225) &&
-               wait_or_abort(bar(vSpEmpty), i & 1, abort_flag, p, 226);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sp(in);
-        }
-      }
-      if (ok) mma_commit(bar(vOutFull));
-    }
-  } else {
-    using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
-    const int r = threadIdx.x;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    const float scale2 = p.scale * kLog2e;
-    bool ok = true;
-    for (int i = 0; i < cnt && ok; ++i) {
-      const int I = J + i;
-      const int gi = I * kBM + r;
-      const bool valid = gi < c.len;
-      const long long slot = ((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * (4 * kBM) + r;
-      const float r1f = p.bnd_r1[slot];
-      const float gpre = p.bnd_s2[slot];
-      const float dr = valid ? load_drem<T>(p, (c.boff * p.heads + h) * p.tokens + c.tok0 + gi) : 0.f;
-      ok = wait_or_abort(bar(vSpFull), i & 1, abort_flag, p, 230);
-      if (ok && i > 0) ok = wait_or_abort(bar(vAzEmpty), (i - 1) & 1, abort_flag, p, 231);
-      if (!ok) break;
-      tc_fence_after();
-      float gs = 0.f, logsum = 0.f;
-      const bool diag = (i == 0);
-      if (diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0))
-        bwd_row_pass<kFp16, true, true>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, diag, p.attend_current, valid,
-                                        scale2, r1f, gpre, dr, gs, logsum, gA, gZ, nullptr, nullptr);
-      else
-        bwd_row_pass<kFp16, true, false>(tS + lane_off, tP + lane_off, bar(vSpEmpty), lane, r, false, 0, true, scale2, r1f, gpre,
-                                         dr, gs, logsum, gA, gZ, nullptr, nullptr);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(vAzFull));
-    }
-    if (ok) ok = wait_or_abort(bar(vOutFull), 0, abort_flag, p, 232);
-    if (ok) {
-      tc_fence_after();
-      const int gj = J * kBM + r;
-      const bool valid = gj < c.len;
-      T *krow_p = reinterpret_cast<T *>(p.dk.ptr) + c.boff * p.dk.sb + (long long)h * p.dk.sh + (c.tok0 + gj) * p.dk.st;
-      T *vrow_p = reinterpret_cast<T *>(p.dv.ptr) + c.boff * p.dv.sb + (long long)h * p.dv.sh + (c.tok0 + gj) * p.dv.st;
-      store_acc_rows<D, kFp16, T>(tDK + lane_off, krow_p, valid, p.head_dim, p.scale);
-      store_acc_rows<D, kFp16, T>(tDV + lane_off, vrow_p, valid, p.head_dim, 1.f);
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
 }
 
 // One row of a 64-key strip: four 16-column chunks, TMEM read one chunk ahead.  mc0: key index of the strip's first
@@ -1296,7 +920,7 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
 }
 
 // -------------------------------------------------------------------------------------------------------
-template <int D, bool kFp16>
+template <bool kFp16>
 static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
   CUtensorMap mq, mk, mv, mg;
   cudaError_t e;
@@ -1305,29 +929,21 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
   if ((e = make_tile_map(&mv, p.v, p, dtype)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mg, p.d_o, p, dtype)) != cudaSuccess) return e;
   const dim3 grid((unsigned)item_blocks(p, 1)), grid_pairs((unsigned)item_blocks(p, 2));
-  CUtensorMap mk64, mv64;   // 64-row boxes for the kernels that stream 64-key sub-tiles
-  if (D == 128) {
-    if ((e = make_tile_map(&mk64, p.k, p, dtype, 64)) != cudaSuccess) return e;
-    if ((e = make_tile_map(&mv64, p.v, p, dtype, 64)) != cudaSuccess) return e;
-  }
-  if (!p.skip_dq && D == 128) {
+  if (!p.skip_dq) {
     auto kernel = tc_bwd_dq2_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq2::kSmem);
     if (e != cudaSuccess) return e;
+    CUtensorMap mk64, mv64;   // 64-row boxes: the kernel streams 64-key sub-tiles
+    if ((e = make_tile_map(&mk64, p.k, p, dtype, 64)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mv64, p.v, p, dtype, 64)) != cudaSuccess) return e;
     CUtensorMap mdq, maz32;   // stores: 32 rows per warp
     if ((e = make_tile_map(&mdq, p.dq, p, dtype, 32)) != cudaSuccess) return e;
     if (p.az != nullptr) { if ((e = make_az_map(&maz32, p, dtype, 32)) != cudaSuccess) return e; }
     else maz32 = mdq;         // not used
     kernel<<<grid_pairs, dq2::kThreads, dq2::kSmem, s>>>(mq, mk64, mv64, mg, mdq, maz32, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  } else if (!p.skip_dq) {
-    auto kernel = tc_bwd_dq_kernel<D, kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::kSmem);
-    if (e != cudaSuccess) return e;
-    kernel<<<grid, kTcThreads, DqCfg<D>::kSmem, s>>>(mq, mk, mv, mg, p);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
-  if (!p.skip_dkv && D == 128 && p.az != nullptr) {
+  if (!p.skip_dkv && p.az != nullptr) {
     auto kernel = tc_bwd_dkv5_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv5::kSmem);
     if (e != cudaSuccess) return e;
@@ -1339,7 +955,7 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     if ((e = make_tile_map(&mdv, p.dv, p, dtype, 32)) != cudaSuccess) return e;
     kernel<<<grid, dkv5::kThreads, dkv5::kSmem, s>>>(maz, mq64, mg64, mdk, mdv, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  } else if (!p.skip_dkv && D == 128) {
+  } else if (!p.skip_dkv) {
     auto kernel = tc_bwd_dkv4_kernel<kFp16>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv4::kSmem);
     if (e != cudaSuccess) return e;
@@ -1348,24 +964,15 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     if ((e = make_tile_map(&mdv, p.dv, p, dtype, 64)) != cudaSuccess) return e;
     kernel<<<grid, dkv4::kThreads, dkv4::kSmem, s>>>(mq, mk, mv, mg, mdk, mdv, p);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  } else if (!p.skip_dkv) {
-    auto kernel = tc_bwd_dkv_kernel<D, kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::kSmem);
-    if (e != cudaSuccess) return e;
-    kernel<<<grid, kTcThreads, DkvCfg<D>::kSmem, s>>>(mq, mk, mv, mg, p);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   return cudaSuccess;
 }
 
+// Every head size up to 128 runs the same 128-column kernels: TMA fills the columns past head_dim with zeros, and the
+// row passes, which bound these kernels, do not depend on the head size.
 cudaError_t launch_tc_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches) {
   *launches += (p.skip_dq ? 0 : 1) + (p.skip_dkv ? 0 : 1);
-  const bool f16 = dtype == SB_DTYPE_F16;
-  // Head sizes up to 64 run the 128-column kernels too: TMA fills the missing columns with zeros, and the row passes,
-  // which bound these kernels, do not depend on the head size (the 64-column kernels above are the earlier design:
-  // one tile per block, no stored tiles; measured 20 % slower).
-  if (p.head_dim <= 64 && p.dbg == 64) return f16 ? launch_bwd_t<64, true>(p, dtype, s) : launch_bwd_t<64, false>(p, dtype, s);
-  return f16 ? launch_bwd_t<128, true>(p, dtype, s) : launch_bwd_t<128, false>(p, dtype, s);
+  return dtype == SB_DTYPE_F16 ? launch_bwd_t<true>(p, dtype, s) : launch_bwd_t<false>(p, dtype, s);
 }
 
 }  // namespace sb
