@@ -26,7 +26,7 @@ static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; 
 //   packed batches: [order int2 x tiles][order2 (backward) int2 x tiles]
 //   backward, either: [A | dz tiles, 16-bit x chunk_heads x pairs_cap x 2 x 128 x 128]   (stored-tiles mode)
 //             or:     [R1 fp32 x chunk_heads x pairs_cap x halves x tile][S2 same]       (recompute mode)
-//   backward with SB_FLAG_FUSE_REM_V: [d_rem + <d_out, v>, fp32 x batch x heads x tokens]
+//   backward with SB_FLAG_FUSE_REM_V: [d_rem + <d_out, v>, one value of the tensors' dtype in a 4-byte slot budget x batch x heads x tokens]
 struct Plan {
   int path;
   int tile;
@@ -205,7 +205,7 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   }
   k.pairs_cap = pl.pairs_cap;
   k.fuse_rem_v = (p->flags & SB_FLAG_FUSE_REM_V) ? 1 : 0;
-  if (backward && k.fuse_rem_v) k.drem_f32 = reinterpret_cast<float *>(ws + pl.off_drem);
+  if (backward && k.fuse_rem_v) k.d_rem_fused = ws + pl.off_drem;
   k.status = p->status;
   return SB_OK;
 }
@@ -228,6 +228,7 @@ static int run(const SbParams *p, void *stream, bool backward) {
     e = launch_fused_drem(k, p->dtype, s);
     g_launches += 1;
     if (e != cudaSuccess) return fail(SB_ERR_CUDA, "d_rem launch: %s", cudaGetErrorString(e));
+    k.d_rem = k.d_rem_fused;   // what the backward kernels read from here on
   }
   const int chunk = backward ? pl.chunk_heads : p->heads;
   for (int h0 = 0; h0 < p->heads; h0 += chunk) {

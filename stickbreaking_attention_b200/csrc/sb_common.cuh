@@ -53,7 +53,8 @@ struct KParams {
   unsigned short *az;  // stored-tiles mode: [head_cnt][pairs_cap][A, dz][128 query rows][128 keys], 16-bit; else null
   long long pairs_cap;
   int fuse_rem_v;      // forward writes o + rem * v; backward folds the two extra gradient terms in
-  float *drem_f32;     // backward with fuse_rem_v: [batch][heads][tokens] d_rem + <d_out, v>, else nullptr
+  char *d_rem_fused;   // backward with fuse_rem_v: [batch][heads][tokens] d_rem + <d_out, v> in the tensors' dtype,
+                       // written by the first kernel of the call; `d_rem` then points here for the other kernels
   int *status;
 };
 
@@ -142,11 +143,11 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return
 // Upstream gradient of rem for row `idx` of the (batch, heads, tokens) array.
 template <typename T>
 __device__ __forceinline__ float load_drem(const KParams &p, long long idx) {
-  return p.drem_f32 != nullptr ? p.drem_f32[idx] : to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]);
+  return to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[idx]);
 }
 
 // Host-side launch helpers implemented in the .cu files; all return cudaError_t of the launch.
-cudaError_t launch_fused_drem(const KParams &p, int dtype, cudaStream_t s);   // fills drem_f32 (all heads)
+cudaError_t launch_fused_drem(const KParams &p, int dtype, cudaStream_t s);   // fills d_rem_fused (all heads)
 cudaError_t launch_fused_dv(const KParams &p, int dtype, cudaStream_t s);     // dv += rem * d_out (all heads)
 cudaError_t launch_prep(const KParams &p, cudaStream_t s);
 cudaError_t launch_zero_tail(const KParams &p, int dtype, bool backward, cudaStream_t s);

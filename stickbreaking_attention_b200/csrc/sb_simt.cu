@@ -209,7 +209,8 @@ __global__ void __launch_bounds__(256) fused_drem_kernel(KParams p, int group) {
   for (int o = group >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if (tok < p.tokens && x0 == 0) {
     const long long row = (b * p.heads + h) * p.tokens + tok;
-    p.drem_f32[row] = s + (p.d_rem != nullptr ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[row]) : 0.f);
+    reinterpret_cast<T *>(p.d_rem_fused)[row] =
+        from_f32<T>(s + (p.d_rem != nullptr ? to_f32<T>(reinterpret_cast<const T *>(p.d_rem)[row]) : 0.f));
   }
 }
 
