@@ -199,6 +199,16 @@ __device__ __forceinline__ void mma_kmajor_mnmajor(uint32_t d_tmem, uint32_t a_a
   for (int ks = 0; ks < KDIM / 16; ++ks)
     mma_f16_ss(d_tmem, a0 + kstep_kmajor(ks, kBoxBytes), b0 + (uint64_t)(ks * 128), idesc, accumulate || ks > 0);
 }
+// A: [128 x KDIM] 16-bit rows in tensor memory (KDIM / 2 columns starting at a_tmem, two K elements per column);
+// B as in mma_kmajor_mnmajor.
+template <int KDIM, int B_BOX = kBoxBytes>
+__device__ __forceinline__ void mma_tmem_mnmajor(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
+                                                 bool accumulate) {
+  const uint64_t b0 = smem_desc_sw128(b_addr, B_BOX, 1024);
+#pragma unroll
+  for (int ks = 0; ks < KDIM / 16; ++ks)
+    mma_f16_ts(d_tmem, a_tmem + ks * 8, b0 + (uint64_t)(ks * 128), idesc, accumulate || ks > 0);
+}
 // A and B both stored with rows = K (128): A^T B.
 __device__ __forceinline__ void mma_mnmajor_mnmajor(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
                                                     bool accumulate) {

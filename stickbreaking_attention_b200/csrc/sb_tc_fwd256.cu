@@ -21,6 +21,17 @@ constexpr int kMaxStages = 6;
 constexpr int kKvBoxBytes = kBN * 64 * 2;     // one 64-row x 64-column box
 constexpr int kPBytes = kBM * kBN * 2;        // one P buffer: 128 rows x 64 keys
 constexpr int kBarBytes = 512;
+// P, the 16-bit A operand of O += P V, goes to the second MMA through tensor memory: the row threads write their
+// packed row into columns 32..63 of the very S slot they have just read (key k of the step in column 32 + k / 2;
+// the chunks are read last column first, so every column written has been read before), and the MMA takes its A
+// operand from there.  The next S MMA into that slot is issued by the same thread after this P V MMA, and MMAs of
+// one thread execute in order.  With SB_FWD_P_SMEM the earlier hand-over through a swizzled shared-memory tile is built.
+#ifdef SB_FWD_P_SMEM
+constexpr bool kPTmem = false;
+#else
+constexpr bool kPTmem = true;
+#endif
+constexpr uint32_t kPCol = 32;
 template <int D>                              // D: head size rounded up to 64 or 128
 struct Cfg {
   static constexpr int kBoxes = D / 64;                        // 64-column blocks per row
@@ -45,9 +56,11 @@ static_assert(bKvEmpty - bKvFull == kMaxStages && bSFull - bKvEmpty == kMaxStage
 // R carries that product over everything after the current column.  Four columns share one reciprocal and one
 // logarithm of t0 t1 t2 t3; the four inclusive products follow from R, that reciprocal and partial products with
 // five multiplications, and beta itself is never formed.
+using fwd256::kPTmem;
 template <bool kFp16, bool kMasked>
 __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0, int key0, int row, int ac,
-                                                 float scale2, float &R, float &logsum, uint8_t *tile_p, int r) {
+                                                 float scale2, float &R, float &logsum, uint8_t *tile_p, int r,
+                                                 uint32_t tmem_p) {
   float pr[16];
   const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
 #pragma unroll
@@ -79,22 +92,28 @@ __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0
     pr[4 * g + 2] = q23.x;
     pr[4 * g + 3] = q23.y;
   }
-  store_row_chunk16<kFp16>(tile_p, r, c0, pr);
+  if constexpr (kPTmem) {   // 16 keys = 8 packed columns of this row's lane
+    uint32_t w[8];
+    pack_row_chunk16<kFp16>(pr, w);
+    tmem_st8(tmem_p + (c0 >> 1), w);
+  } else {
+    store_row_chunk16<kFp16>(tile_p, r, c0, pr);
+  }
 }
 
 template <bool kFp16, bool kMasked>
 __device__ __forceinline__ void fwd256_row_pass(uint32_t ts, int key0, int row, int ac, float scale2, float &R,
-                                                float &logsum, uint8_t *tile_p, int r) {
+                                                float &logsum, uint8_t *tile_p, int r, uint32_t tmem_p) {
   uint32_t va[16], vb[16];
   tmem_ld16(ts + 48, va);
 #pragma unroll 1
   for (int pair = 1; pair >= 0; --pair) {
     tmem_wait_ld_regs(va);
     tmem_ld16(ts + pair * 32, vb);
-    fwd256_row_chunk<kFp16, kMasked>(va, pair * 32 + 16, key0 + pair * 32 + 16, row, ac, scale2, R, logsum, tile_p, r);
+    fwd256_row_chunk<kFp16, kMasked>(va, pair * 32 + 16, key0 + pair * 32 + 16, row, ac, scale2, R, logsum, tile_p, r, tmem_p);
     tmem_wait_ld_regs(vb);
     if (pair == 1) tmem_ld16(ts + 16, va);
-    fwd256_row_chunk<kFp16, kMasked>(vb, pair * 32, key0 + pair * 32, row, ac, scale2, R, logsum, tile_p, r);
+    fwd256_row_chunk<kFp16, kMasked>(vb, pair * 32, key0 + pair * 32, row, ac, scale2, R, logsum, tile_p, r, tmem_p);
   }
 }
 
@@ -262,9 +281,14 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             trace_event(p, 1 + 3 * wg, tr_cur, 6 + 16 * wg, t0 + up);
             tc_fence_after();
             // 16 keys per MMA; V: 64 rows x (2 x 64) columns, MN-major
-            mma_kmajor_mnmajor<kBN, kKvBoxBytes>(tmem + 256 + wg * 128, sP + (wg * 2 + (gu & 1)) * kPBytes,
+            if constexpr (kPTmem) {
+              mma_tmem_mnmajor<kBN, kKvBoxBytes>(tmem + 256 + wg * 128, tmem + wg * 128 + (gu & 1) * 64 + kPCol,
                                                  sKV + st * kStageBytes + kKvTileBytes, idesc_pv, up > 0);
-            mma_commit(bar(bPEmpty + wg * 2 + (gu & 1)));
+            } else {
+              mma_kmajor_mnmajor<kBN, kKvBoxBytes>(tmem + 256 + wg * 128, sP + (wg * 2 + (gu & 1)) * kPBytes,
+                                                   sKV + st * kStageBytes + kKvTileBytes, idesc_pv, up > 0);
+              mma_commit(bar(bPEmpty + wg * 2 + (gu & 1)));
+            }
             mma_commit(bar(bKvEmpty + st));
             trace_event(p, 1 + 3 * wg, tr_cur, 7 + 16 * wg, t0 + up);
           }
@@ -302,7 +326,9 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int s = w.s_top - (t0 + u);
         const int gu = U + u, buf = gu & 1;
         ok = wait_or_abort(bar(bSFull + wg * 2 + buf), (gu >> 1) & 1, abort_flag, p, 330);
-        if (ok && gu >= 2) ok = wait_or_abort(bar(bPEmpty + wg * 2 + buf), ((gu >> 1) - 1) & 1, abort_flag, p, 331);
+        // a shared-memory P buffer is free once the P V MMA of two steps ago has read it; P in tensor memory needs no
+        // such wait: it overwrites scores of this very step, which the same thread has already loaded
+        if (!kPTmem && ok && gu >= 2) ok = wait_or_abort(bar(bPEmpty + wg * 2 + buf), ((gu >> 1) - 1) & 1, abort_flag, p, 331);
         if (!ok) break;
         if (threadIdx.x == 128 && u == 0 && it == 0) trace_block(p, 1);
         if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 4 + 16 * wg, t0 + u);
@@ -312,11 +338,12 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         float R = ex2(-(float)run);
         float logsum = 0.f;
         // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
-        if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r);
-        else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r);
+        if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
+        else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
         run += (double)logsum;
-        tc_fence_before();          // this step's TMEM reads are done before the slot is handed back
-        fence_proxy_async_smem();
+        if constexpr (kPTmem) tmem_wait_st();
+        tc_fence_before();          // this step's TMEM reads (and writes of P) are done before the slot is handed back
+        if constexpr (!kPTmem) fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(bPFull + wg * 2 + buf));
         if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 5 + 16 * wg, t0 + u);
