@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define SB_ABI_VERSION 1
+#define SB_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define SB_EXPORT __attribute__((visibility("default")))
@@ -46,7 +46,10 @@ enum SbStatus {
 enum SbDeviceStatus {
   SB_DEV_OK = 0,
   SB_DEV_BAD_CU_SEQLENS = 1, /* not non-decreasing, beyond `tokens`, or longer than max_seqlen;
-                                status[1] = index of the offending sequence                    */
+                                status[1] = index of the offending sequence.  No kernel of the
+                                call then computes anything, and every row of the call's outputs
+                                is filled with NaN (where the reference raises on the host,
+                                sb_varlen/__init__.py:72-74)                                   */
   SB_DEV_WAIT_TIMEOUT = 2    /* a bounded on-chip wait gave up; status[1] = which barrier      */
 };
 
@@ -67,10 +70,11 @@ enum SbFlags {
                             what a previous full sb_bwd left in the same workspace              */
   SB_FLAG_BWD_RECOMPUTE = 16, /* small-workspace backward.  By default (16-bit tensors, head_dim up to 128)
                             the dQ kernel stores its A and dz tiles -- 64 KiB per (query tile, key tile)
-                            pair and head, heads processed in chunks of at most 8 GiB -- and the dK/dV
-                            kernel is two plain GEMMs over them.  With this flag, or when one head
-                            exceeds 8 GiB, the dK/dV kernel recomputes the tiles from boundary values
-                            (a few KiB per pair).  Same 16-bit tiles either way.                 */
+                            pair and head, heads processed in chunks that fit the scratch budget (8 GiB
+                            unless sb_set_backward_scratch_budget changed it) -- and the dK/dV kernel is
+                            two plain GEMMs over them.  With this flag, or when one head alone exceeds the
+                            budget, the dK/dV kernel recomputes the tiles from boundary values (a few KiB
+                            per pair).  Same 16-bit tiles either way.                             */
   SB_FLAG_FUSE_REM_V = 32   /* the caller wants out = o + rem[..., None] * v, what every caller of the
                             reference computes right after the operator (tests/test_varlen.py:101,
                             tests/test_attn.py:64).  sb_fwd writes `out` to `o` (rem and log_rem as usual).
@@ -99,9 +103,7 @@ typedef struct SbParams {
   int32_t cu_seqlens_int64; /* element type of cu_seqlens: 0 = int32, 1 = int64                 */
   float logit_scale;    /* multiplies <q,k>; the reference default is 1/sqrt(head_dim)          */
   int32_t flags;        /* SbFlags                                                              */
-  int32_t reserved;     /* 0.  Diagnostics: 0x100 makes sb_workspace_bytes() 128 KiB larger; in a library built  *
-                         * with -DSB_TRACE, block (0,0) of the tensor-core kernels logs (event, SM clock)   *
-                         * pairs per role into that tail                                                    */
+  int32_t reserved;     /* must be 0                                                            */
   const void *cu_seqlens; /* device, num_seq sequence END offsets, or NULL                      */
 
   SbTensor q, k, v;     /* in                                                                    */
@@ -118,6 +120,15 @@ typedef struct SbParams {
   void *workspace;      /* device scratch of at least sb_workspace_bytes() bytes, 256-B aligned  */
   size_t workspace_bytes;
   int32_t *status;      /* device int32[4], zeroed by the caller, or NULL                        */
+
+  float *attn_weights;  /* optional out (forward), NULL otherwise: fp32 (batch, heads, tokens, attn_cols)  *
+                         * contiguous and ZEROED by the caller.  Row t receives the attention weights of   *
+                         * token t, entry j being the weight on the j-th key of t's own sequence (j <      *
+                         * attn_cols).  This is the `return_attention` / W output the reference marks TODO *
+                         * (sb_varlen_fwd.py:195-202, 421-425): same fp32, caller-zeroed, sequence-local   *
+                         * key index.  A debugging aid: the call then runs the CUDA-core kernels, whatever *
+                         * the dtype.                                                                       */
+  int64_t attn_cols;    /* columns of attn_weights (>= the longest sequence to get every weight)          */
 } SbParams;
 
 /* Scratch bytes sb_fwd (backward == 0) or sb_bwd (backward != 0) needs for these shapes.  Looks at
@@ -148,11 +159,12 @@ SB_EXPORT int sb_bwd(const SbParams *p, void *stream);
  * of SB_STATIC_SCRATCH_BYTES bytes inside the library's device image.  Every GPU that loads the library holds
  * that array until the process exits.
  *
- * Same results as sb_fwd.  Calls that need more scratch than the array holds (sb_workspace_bytes(p, 0) >
- * SB_STATIC_SCRATCH_BYTES; a packed batch needs about 20 bytes per sequence plus 8 bytes per 128 tokens, so
- * e.g. 2500 sequences in 65536 tokens fit; a fixed-length batch always fits) return SB_ERR_WORKSPACE with a
- * message and launch nothing.  The function calls no cudaMalloc, cudaFree or any
- * other allocating routine.
+ * Same results as sb_fwd.  A call fits when sb_workspace_bytes(p, 0) <= SB_STATIC_SCRATCH_BYTES; that is the whole
+ * rule.  (The scratch holds the sequence table: a few hundred bytes plus about 12 bytes per packed sequence and 8
+ * bytes per work item, an item being 256 tokens on the tensor-core path and 32 tokens on the CUDA-core path that
+ * fp32 tensors and irregular head sizes take; a fixed-length batch always fits.)  A call that does not fit returns
+ * SB_ERR_WORKSPACE with a message and launches nothing.  The function calls no cudaMalloc, cudaFree or any other
+ * allocating routine.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call before any stream capture begins.  All calls on a device share the one
@@ -160,6 +172,14 @@ SB_EXPORT int sb_bwd(const SbParams *p, void *stream);
  * whose kernels may overlap on the GPU (different streams, or different threads) race on it: serialise them. */
 #define SB_STATIC_SCRATCH_BYTES 65536
 SB_EXPORT int sb_fwd_static_scratch(const SbParams *p, void *stream);
+
+/* Upper bound, in bytes, on the scratch one chunk of heads of sb_bwd may take (default 8 GiB); returns the previous
+ * value, and with bytes == 0 only reports it.  Process-wide; affects sb_workspace_bytes(p, 1) and sb_bwd alike, so
+ * set it before sizing a workspace.  The backward works through the heads in chunks whose stored attention tiles
+ * (64 KiB per 128 x 128 tile pair and head) fit the bound, and takes the recomputing dK/dV kernel when one head alone
+ * does not fit.  The reference has no counterpart: its backward keeps nothing but lock arrays
+ * (sb_varlen_bwd.py:568-573). */
+SB_EXPORT size_t sb_set_backward_scratch_budget(size_t bytes);
 
 /* Which kernels sb_fwd / sb_bwd run for these parameters (an SbKernelPath), or -1 if invalid. */
 SB_EXPORT int sb_kernel_path(const SbParams *p);

@@ -24,8 +24,9 @@ SB_DEV_MESSAGES = {
        "or without its leading zero); offending sequence index: {0}",
     2: "a bounded on-chip wait timed out in barrier {0}",
 }
-EXPORTS = ("sb_workspace_bytes", "sb_fwd", "sb_bwd", "sb_fwd_static_scratch", "sb_kernel_path", "sb_last_launch_count",
-           "sb_last_error", "sb_abi_version")
+EXPORTS = ("sb_workspace_bytes", "sb_fwd", "sb_bwd", "sb_fwd_static_scratch", "sb_set_backward_scratch_budget",
+           "sb_kernel_path", "sb_last_launch_count", "sb_last_error", "sb_abi_version")
+ABI_VERSION = 2
 
 
 class SbTensor(ctypes.Structure):
@@ -45,6 +46,7 @@ class SbParams(ctypes.Structure):
         ("d_o", SbTensor), ("d_rem", ctypes.c_void_p),
         ("dq", SbTensor), ("dk", SbTensor), ("dv", SbTensor),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t), ("status", ctypes.c_void_p),
+        ("attn_weights", ctypes.c_void_p), ("attn_cols", ctypes.c_int64),
     ]
 
 
@@ -75,9 +77,12 @@ def load(path: str | None = None) -> ctypes.CDLL:
     lib.sb_kernel_path.argtypes = [ctypes.POINTER(SbParams)]
     lib.sb_last_launch_count.restype = ctypes.c_int
     lib.sb_last_error.restype = ctypes.c_char_p
+    lib.sb_set_backward_scratch_budget.restype = ctypes.c_size_t
+    lib.sb_set_backward_scratch_budget.argtypes = [ctypes.c_size_t]
     lib.sb_abi_version.restype = ctypes.c_int
-    if lib.sb_abi_version() != 1:
-        raise SbError(f"{path}: ABI version {lib.sb_abi_version()} but this binding speaks 1")
+    if lib.sb_abi_version() != ABI_VERSION:
+        raise SbError(f"{path}: ABI version {lib.sb_abi_version()} but this binding speaks {ABI_VERSION}; "
+                      "rebuild with `python stickbreaking_attention_b200/build.py --force`")
     _lib = lib
     return lib
 

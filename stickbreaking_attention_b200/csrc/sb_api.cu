@@ -1,4 +1,5 @@
 // C ABI of the library: argument checks, workspace layout, kernel selection, launches.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -43,7 +44,10 @@ struct Plan {
   size_t total_fwd, total_bwd;
 };
 
-constexpr size_t kBoundaryBudget = (size_t)8 << 30;  // scratch for R1 + S2 before heads are chunked
+// Upper bound on the backward's per-chunk scratch (stored tiles, or R1 + S2): heads are processed in chunks that fit
+// it, and a call whose single head does not fit the stored tiles takes the recomputing dK/dV kernel.  Process-wide,
+// set through sb_set_backward_scratch_budget.
+static std::atomic<size_t> g_scratch_budget{(size_t)8 << 30};
 
 static int check_tensor(const SbTensor &t, const char *name, bool required) {
   if (t.ptr == nullptr) return required ? fail(SB_ERR_ARGUMENT, "%s.ptr is NULL", name) : SB_OK;
@@ -75,7 +79,8 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   if (p->max_seqlen < 0) return fail(SB_ERR_ARGUMENT, "max_seqlen is negative");
 
   const int esize = p->dtype == SB_DTYPE_F32 ? 4 : 2;
-  bool tc = !(p->flags & SB_FLAG_FORCE_SIMT) && tc_supported(p->dtype, p->head_dim, backward) &&
+  bool tc = !(p->flags & SB_FLAG_FORCE_SIMT) && !(p->attn_weights != nullptr && !backward) &&
+            tc_supported(p->dtype, p->head_dim, backward) &&
             tma_friendly(p->q, esize) && tma_friendly(p->k, esize) && tma_friendly(p->v, esize);
   // outputs and gradients are stored with 16-byte vectors on the tensor-core path
   const SbTensor *others[] = {&p->o, &p->d_o, &p->dq, &p->dk, &p->dv};
@@ -107,15 +112,20 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   pl.bnd_bytes_per_head = align_up((size_t)pl.pairs_cap * pl.tile * pl.bnd_halves * sizeof(float), 256);
   // Stored-tiles mode (128-column head sizes): 64 KiB per (query tile, key tile) pair and head.  Taken when at least one
   // head fits the budget and the caller did not ask for the small-workspace mode.
+  const size_t budget = g_scratch_budget.load(std::memory_order_relaxed);
   pl.az_bytes_per_head = (size_t)pl.pairs_cap * 2 * kTcTile * kTcTile * 2;
-  pl.store_az = backward && tc && !(p->flags & SB_FLAG_BWD_RECOMPUTE) &&
-                pl.az_bytes_per_head <= kBoundaryBudget;
+  pl.store_az = backward && tc && !(p->flags & SB_FLAG_BWD_RECOMPUTE) && pl.az_bytes_per_head <= budget;
   const size_t per_head = pl.store_az ? pl.az_bytes_per_head : 2 * pl.bnd_bytes_per_head;
-  size_t chunk = per_head ? kBoundaryBudget / per_head : (size_t)p->heads;
+  size_t chunk = per_head ? budget / per_head : (size_t)p->heads;
   if (chunk < 1) chunk = 1;
   if (chunk > (size_t)p->heads) chunk = p->heads;
   pl.chunk_heads = (int)chunk;
-  const size_t trace_bytes = (p->reserved & 0x100) ? kTraceBytes : 0;   // experiments only
+#ifdef SB_TRACE   // diagnostic builds: reserved & 0x100 appends the event log to the workspace
+  const size_t trace_bytes = (p->reserved & 0x100) ? kTraceBytes : 0;
+#else
+  if (p->reserved != 0) return fail(SB_ERR_ARGUMENT, "reserved must be 0");
+  const size_t trace_bytes = 0;
+#endif
   pl.total_fwd = pl.off_bnd + trace_bytes;
   pl.off_drem = align_up(pl.off_bnd + per_head * chunk, 256);
   const size_t drem_bytes =
@@ -179,13 +189,17 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   k.attend_current = p->attend_current ? 1 : 0;
   k.scale = p->logit_scale;
   k.check_leading_zero = (p->cu_seqlens != nullptr && (p->flags & SB_FLAG_CHECK_LEADING_ZERO)) ? 1 : 0;
-  k.dbg = p->reserved & 0xff;
   // Tiles of one sequence that stay neighbours in the launch order.  The backward kernels gain more from sharing
   // K/V or Q/dO reads through L2 (measured: -4 % at 2048-token, -8 % at 4096-token sequences) than they lose in the
   // tail; the forward's blocks are persistent with a fixed item assignment, which wants the pure weight order.
   k.order_span = backward ? 16 : 1;
+#ifdef SB_TRACE
+  k.dbg = p->reserved & 0xff;
   k.trace_mode = (p->reserved >> 8) & 3;
   k.trace = (p->reserved & 0x100) ? reinterpret_cast<unsigned long long *>(ws_end - kTraceBytes) : nullptr;
+#else
+  (void)ws_end;
+#endif
   k.skip_dq = (p->flags & SB_FLAG_BWD_SKIP_DQ) ? 1 : 0;
   k.skip_dkv = (p->flags & SB_FLAG_BWD_SKIP_DKV) ? 1 : 0;
   k.tile = pl.tile; k.tiles_cap = pl.tiles_cap; k.n_max = pl.n_max; k.max_seqlen = pl.max_seqlen;
@@ -205,6 +219,11 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
   }
   k.pairs_cap = pl.pairs_cap;
   k.fuse_rem_v = (p->flags & SB_FLAG_FUSE_REM_V) ? 1 : 0;
+  if (!backward && p->attn_weights != nullptr) {
+    if (p->attn_cols < 1) return fail(SB_ERR_ARGUMENT, "attn_cols must be >= 1 with attn_weights");
+    k.attn = p->attn_weights;
+    k.attn_cols = p->attn_cols;
+  }
   if (backward && k.fuse_rem_v) k.d_rem_fused = ws + pl.off_drem;
   k.status = p->status;
   return SB_OK;
@@ -287,7 +306,7 @@ static int run_fwd_static_scratch(const SbParams *p, void *stream) {
   if (pl.total_fwd > (size_t)SB_STATIC_SCRATCH_BYTES)
     return fail(SB_ERR_WORKSPACE,
                 "sb_fwd_static_scratch: this call needs %zu bytes of scratch but the built-in scratch holds %d "
-                "(about 20 bytes per packed sequence plus 8 per 128 tokens); use sb_fwd with a caller-provided workspace",
+                "(sb_workspace_bytes(p, 0) is the measure); use sb_fwd with a caller-provided workspace",
                 pl.total_fwd, (int)SB_STATIC_SCRATCH_BYTES);
   if ((rc = device_ok())) return rc;
   void *scratch = nullptr;
@@ -323,6 +342,11 @@ int sb_last_launch_count(void) { return sb::g_launches; }
 const char *sb_last_error(void) { return sb::g_err; }
 
 int sb_fwd_static_scratch(const SbParams *p, void *stream) { return sb::run_fwd_static_scratch(p, stream); }
+
+size_t sb_set_backward_scratch_budget(size_t bytes) {
+  if (bytes == 0) return sb::g_scratch_budget.load(std::memory_order_relaxed);
+  return sb::g_scratch_budget.exchange(bytes, std::memory_order_relaxed);
+}
 
 int sb_abi_version(void) { return SB_ABI_VERSION; }
 

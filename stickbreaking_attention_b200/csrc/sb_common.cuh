@@ -52,6 +52,8 @@ struct KParams {
   float *bnd_s2;       // [head_cnt][pairs_cap][tile]  prefix sums of G before each key tile
   unsigned short *az;  // stored-tiles mode: [head_cnt][pairs_cap][A, dz][128 query rows][128 keys], 16-bit; else null
   long long pairs_cap;
+  float *attn;         // forward, CUDA-core kernels only: [batch][heads][tokens][attn_cols] attention weights, or null
+  long long attn_cols;
   int fuse_rem_v;      // forward writes o + rem * v; backward folds the two extra gradient terms in
   char *d_rem_fused;   // backward with fuse_rem_v: [batch][heads][tokens] d_rem + <d_out, v> in the tensors' dtype,
                        // written by the first kernel of the call; `d_rem` then points here for the other kernels

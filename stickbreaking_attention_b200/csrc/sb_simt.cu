@@ -149,26 +149,30 @@ cudaError_t launch_prep(const KParams &p, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-// Rows past the end of the last packed sequence belong to no sequence: write zeros there.
+// Rows past the end of the last packed sequence belong to no sequence: write zeros there.  When the sequence table
+// was refused (bad cu_seqlens: every other kernel of the call has returned at once), every row of the outputs is
+// filled with NaN instead, so that a caller who does not look at the status word cannot mistake uninitialised memory
+// for results.
 template <typename T>
 __global__ void zero_tail_kernel(KParams p, bool backward) {
-  if (p.hdr[0]) return;
-  const long long first = p.hdr[1];
+  const bool refused = p.hdr[0] != 0;
+  const long long first = refused ? 0 : p.hdr[1];
+  const float fill = refused ? __int_as_float(0x7fc00000) : 0.f;
   const int h = p.head0 + blockIdx.y;
   const int d = p.head_dim;
   for (long long row = first + blockIdx.x; row < p.tokens; row += gridDim.x) {
     if (!backward) {
       T *o = reinterpret_cast<T *>(p.o.ptr) + h * p.o.sh + row * p.o.st;
-      for (int x = threadIdx.x; x < d; x += blockDim.x) o[x] = from_f32<T>(0.f);
+      for (int x = threadIdx.x; x < d; x += blockDim.x) o[x] = from_f32<T>(fill);
       if (threadIdx.x == 0) {
-        reinterpret_cast<T *>(p.rem)[(long long)h * p.tokens + row] = from_f32<T>(0.f);
-        p.log_rem[(long long)h * p.tokens + row] = 0.0;
+        reinterpret_cast<T *>(p.rem)[(long long)h * p.tokens + row] = from_f32<T>(fill);
+        p.log_rem[(long long)h * p.tokens + row] = (double)fill;
       }
     } else {
       T *a = reinterpret_cast<T *>(p.dq.ptr) + h * p.dq.sh + row * p.dq.st;
       T *b = reinterpret_cast<T *>(p.dk.ptr) + h * p.dk.sh + row * p.dk.st;
       T *c = reinterpret_cast<T *>(p.dv.ptr) + h * p.dv.sh + row * p.dv.st;
-      for (int x = threadIdx.x; x < d; x += blockDim.x) { a[x] = b[x] = c[x] = from_f32<T>(0.f); }
+      for (int x = threadIdx.x; x < d; x += blockDim.x) { a[x] = b[x] = c[x] = from_f32<T>(fill); }
     }
   }
 }
@@ -277,7 +281,7 @@ cudaError_t launch_fused_dv(const KParams &p, int dtype, cudaStream_t s) {
 
 cudaError_t launch_zero_tail(const KParams &p, int dtype, bool backward, cudaStream_t s) {
   if (p.cu == nullptr) return cudaSuccess;
-  dim3 grid(8, p.head_cnt);
+  dim3 grid(32, p.head_cnt);
   if (dtype == SB_DTYPE_F32) zero_tail_kernel<float><<<grid, 128, 0, s>>>(p, backward);
   else if (dtype == SB_DTYPE_BF16) zero_tail_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p, backward);
   else zero_tail_kernel<__half><<<grid, 128, 0, s>>>(p, backward);
@@ -358,6 +362,14 @@ __global__ void __launch_bounds__(256) simt_fwd_kernel(KParams p) {
       run_sp += suffix;
     }
     __syncthreads();
+    if (p.attn != nullptr) {   // debugging aid: the attention weights of this tile, keys indexed inside the sequence
+      for (int e = t; e < kT * kT; e += blockDim.x) {
+        const int rr = e / kT, j = e - rr * kT;
+        const int gi = I * kT + rr, gj = J * kT + j;
+        if (gi < c.len && gj < c.len && gj < p.attn_cols)
+          p.attn[((c.boff * p.heads + h) * p.tokens + c.tok0 + gi) * p.attn_cols + gj] = Ss[rr * kLdS + j];
+      }
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int x = cg + 8 * u;

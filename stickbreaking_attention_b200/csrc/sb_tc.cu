@@ -1,4 +1,6 @@
 // Host side of the tensor-core path: TMA tensor maps, which shapes take the path, the forward dispatch.
+#include <cstring>
+
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -20,34 +22,84 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows) {
+// Encoded maps are pure functions of (base, dims, strides, box, type), and a training loop presents the same few
+// tensors again and again (the caching allocator hands the same blocks back), so each thread keeps the maps it has
+// encoded in a small direct-mapped table and skips the driver call on a hit.
+struct MapKey {
+  const void *ptr;
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box_rows;
+  int dtype;
+  bool operator==(const MapKey &o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kMapSlots = 128;
+
+static cudaError_t encode_cached(CUtensorMap *map, const void *ptr, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
+                                 int box_rows, int dtype) {
+  static thread_local MapSlot table[kMapSlots];
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.ptr = ptr;
+  for (int i = 0; i < 4; ++i) key.dims[i] = dims[i];
+  for (int i = 0; i < 3; ++i) key.strides[i] = strides[i];
+  key.box_rows = (cuuint32_t)box_rows;
+  key.dtype = dtype;
+  uint64_t h = (uint64_t)(uintptr_t)ptr * 0x9E3779B97F4A7C15ull;
+  h ^= (dims[1] + 0x1000193u * box_rows + 31u * strides[0] + 17u * strides[1]) * 0xC2B2AE3D27D4EB4Full;
+  MapSlot &slot = table[(h >> 32) % kMapSlots];
+  if (slot.used && slot.key == key) {
+    *map = slot.map;
+    return cudaSuccess;
+  }
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return cudaErrorNotSupported;
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == SB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  slot.key = key;
+  slot.map = *map;
+  slot.used = true;
+  return cudaSuccess;
+}
+
+cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows) {
   const cuuint64_t esz = 2;
   long long sb_el = t.sb > 0 ? t.sb : (t.sh > 0 ? t.sh * p.heads : (long long)p.tokens * p.head_dim);
   long long sh_el = t.sh > 0 ? t.sh : (long long)p.tokens * p.head_dim;
   cuuint64_t dims[4] = {(cuuint64_t)p.head_dim, (cuuint64_t)p.tokens, (cuuint64_t)p.heads, (cuuint64_t)p.batch};
   cuuint64_t strides[3] = {(cuuint64_t)t.st * esz, (cuuint64_t)sh_el * esz, (cuuint64_t)sb_el * esz};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, dtype == SB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-                   t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+  return encode_cached(map, t.ptr, dims, strides, box_rows, dtype);
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is needed once per kernel and device, not once per launch.
+cudaError_t allow_dynamic_smem(const void *kernel, int bytes) {
+  struct Done { const void *kernel; int dev; };
+  static thread_local Done done[64];
+  static thread_local int n_done = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  for (int i = 0; i < n_done; ++i)
+    if (done[i].kernel == kernel && done[i].dev == dev) return cudaSuccess;
+  if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)) != cudaSuccess) return e;
+  if (n_done < 64) done[n_done++] = Done{kernel, dev};
+  return cudaSuccess;
 }
 
 cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype, int box_rows) {
-  EncodeTiledFn enc = encode_fn();
-  if (enc == nullptr) return cudaErrorNotSupported;
   const cuuint64_t tile_bytes = (cuuint64_t)kBM * kBM * 2;
   cuuint64_t dims[4] = {(cuuint64_t)kBM, (cuuint64_t)p.pairs_cap * kBM, 2, (cuuint64_t)p.head_cnt};
   cuuint64_t strides[3] = {(cuuint64_t)kBM * 2, (cuuint64_t)p.pairs_cap * tile_bytes, 2 * (cuuint64_t)p.pairs_cap * tile_bytes};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, dtype == SB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, p.az,
-                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+  return encode_cached(map, p.az, dims, strides, box_rows, dtype);
 }
 
 // The forward for head sizes above 64 works on 256 query rows per CTA (two 128-row tiles sharing the K/V stream).

@@ -255,6 +255,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int steps_b = b_active ? min(2 * Ia + 4, n_sub) : 0;
   const int n_steps = b_active ? steps_b : steps_a;
   const int issuers = b_active ? 2 : 1;
+  int tr_cur = 0;   // cursor of this thread's event-log lane (diagnostics)
 
   if (threadIdx.x == 0) {
     mbar_init(bar(bQG), 1);
@@ -327,12 +328,15 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           ok = wait_or_abort(bar(bSpEmpty + w), u & 1, abort_flag, p, 526) &&
                wait_or_abort(bar(bKvFull + (u + 1) % kStages), ((u + 1) / kStages) & 1, abort_flag, p, 523);
           if (!ok) break;
+          trace_event(p, 1 + 3 * w, tr_cur, 2 + 16 * w, u + 1);
           tc_fence_after();
           issue_sp(u + 1);
+          trace_event(p, 1 + 3 * w, tr_cur, 3 + 16 * w, u + 1);
         }
         // ... then, once its dz tile is written, this step's dQ
         ok = wait_or_abort(bar(bZFull + w), u & 1, abort_flag, p, 522);
         if (!ok) break;
+        trace_event(p, 1 + 3 * w, tr_cur, 6 + 16 * w, u);
         tc_fence_after();
         // dQ += dz K: dz [128 x 64] K-major, K sub-tile [64 keys x (2 x 64) columns] MN-major
         mma_kmajor_mnmajor<kBN, kKvBox>(tDQ, zaddr, sKV + (u % kStages) * kStageBytes, idesc_dq, u > 0);
@@ -371,6 +375,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       ok = wait_or_abort(bar(bSpFull + w), u & 1, abort_flag, p, 530);
       if (!ok) break;
       if (threadIdx.x == 0 && u == 0) trace_block(p, 1);
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 4 + 16 * w, u);
       tc_fence_after();
       // the dz tile is still being read by the previous step's dQ MMAs: waited for inside the pass, before its first store
       const uint32_t gate = u >= 1 ? bar(bZEmpty + w) : 0u, gate_parity = (u - 1) & 1;
@@ -415,9 +420,14 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       r1 += (double)logsum;
       gpre += gs;
+      // the sequence ends inside this sub-tile: its dz columns behind the end are exact zeros, the K rows there are
+      // not this sequence's (see zero_tile_rows) and are cleared before this step's dz K MMA is released
+      if (c.len - u * kBN < kBN)
+        zero_tile_rows(gbase + (sKV - base) + (u % kStages) * kStageBytes, c.len - u * kBN, kBN, 2, kKvBox, r, kBM);
       tc_fence_before();          // this step's TMEM reads are done before the slots are handed back
       fence_proxy_async_smem();
       __syncwarp();
+      if (r == 0) trace_event(p, 2 + w, tr_cur, 5 + 16 * w, u);
       if (lane == 0) {
         mbar_arrive(bar(bZFull + w));
         if (p.az != nullptr) {   // stored-tiles mode: this warp's 32 rows x 64 keys of dz, out of the shared-memory tile
@@ -635,24 +645,29 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float scale2 = p.scale * kLog2e;
     bool ok = true;
     // the per-row start values of a step come from global memory: they are fetched one step ahead
-    auto fetch = [&](int g, float &r1f, float &gpre, float &dr) {
+    // (the gradient of rem stays a raw 16-bit value until the step that uses it, so that nothing in this step depends
+    // on the load)
+    auto fetch = [&](int g, float &r1f, float &gpre, unsigned short &dr_raw) {
       const int I = J + (g >> hshift), quarter = 2 * (g & hshift) + w;   // which 32-key quarter of the 128-key tile
       const int gi = I * kBM + r;
       const long long slot = (((long long)hh * p.pairs_cap + c.pair0 + (long long)I * (I + 1) / 2 + J) * 4 + quarter) * kBM + r;
       r1f = p.bnd_r1[slot];
       gpre = p.bnd_s2[slot];
-      dr = gi < c.len ? load_drem<T>(p, (c.boff * p.heads + h) * p.tokens + c.tok0 + gi) : 0.f;
+      const long long row = (c.boff * p.heads + h) * p.tokens + c.tok0 + min(gi, c.len - 1);
+      dr_raw = reinterpret_cast<const unsigned short *>(p.d_rem)[row];
     };
     uint8_t *gA = gbase + (sAZ - base);
     uint8_t *gZ = gA + kAzBytes;
-    float nr1, ngpre, ndr;
+    float nr1, ngpre;
+    unsigned short ndr;
     fetch(0, nr1, ngpre, ndr);
     for (int g = 0; g < n_steps && ok; ++g) {
       const int u = g >> hshift, hf = g & hshift, slot = g & 1;
       const int I = J + u;
       const int quarter = 2 * hf + w;
       const bool valid = I * kBM + r < c.len;
-      const float r1f = nr1, gpre = ngpre, dr = ndr;
+      const float r1f = nr1, gpre = ngpre;
+      const float dr = valid ? to_f32<T>(*reinterpret_cast<const T *>(&ndr)) : 0.f;
       if (g + 1 < n_steps) fetch(g + 1, nr1, ngpre, ndr);
       ok = wait_or_abort(bar(bSpFull + slot), (g >> 1) & 1, abort_flag, p, 630);
       if (!ok) break;
@@ -692,6 +707,10 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                                          gpre, dr, gs, logsum, gA, gZ);
       else
         bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      // the sequence ends inside this query tile: the A and dz rows behind the end are exact zeros, the Q and dO rows
+      // there are not this sequence's (see zero_tile_rows) and are cleared before this step's MMAs are released
+      if (c.len - I * kBM < kBM)
+        zero_tile_rows(gbase + (sQ - base) + (u & 1) * 2 * kTileBytes, c.len - I * kBM, kBM, 4, kBoxBytes, threadIdx.x, 2 * kBM);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(bAzFull));
@@ -782,7 +801,7 @@ constexpr int kBox = 64 * 64 * 2;            // 64 rows x 64 columns, 16-bit
 constexpr int kStageBytes = 8 * kBox;        // A, dz, Q, dO: two 64-column blocks each
 constexpr int kSmem = 1024 + kStages * kStageBytes + 512;
 constexpr uint32_t kCols = 256;              // dK 0..127, dV 128..255
-enum { bFull = 0, bEmpty = 3, bOut = 6, bNum = 7 };
+enum { bFull = 0, bEmpty = 3, bOut = 6, bClean = 7, bLanded = 8, bNum = 9 };
 }  // namespace dkv5
 
 template <bool kFp16>
@@ -800,6 +819,13 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
   const int h = p.head0 + hh;
   const int J = c.idx;                        // the 128-key tile
   const int n_stages = 2 * (c.n_tiles - J);   // stage t: query tile J + (t >> 1), rows (t & 1) * 64 .. + 64
+  // The sequence may end inside the last query tile.  The A and dz rows behind the end are zeros in the workspace; the
+  // Q and dO rows there are not this sequence's (see zero_tile_rows).  Stages from t_clean on hold such rows: the
+  // issuer tells the epilogue warps, idle until the end, that such a stage has landed (bLanded; a barrier of its own,
+  // because a parity wait on bFull only works for a waiter that follows every phase), they clear the rows and hand
+  // the stage back through bClean.
+  const int last_rows = c.len - (c.n_tiles - 1) * kBM;          // 1 .. 128 rows of the last query tile exist
+  const int t_clean = last_rows >= kBM ? n_stages : (last_rows > 64 ? n_stages - 1 : n_stages - 2);
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -813,6 +839,8 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(bar(bFull + s), 1); mbar_init(bar(bEmpty + s), 1); }
     mbar_init(bar(bOut), 1);
+    mbar_init(bar(bClean), 4);
+    mbar_init(bar(bLanded), 1);
     ctl->abort = 0;
     fence_barrier_init();
   }
@@ -854,6 +882,10 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
       for (int t = 0; ok && t < n_stages; ++t) {
         const int st = t % kStages;
         ok = wait_or_abort(bar(bFull + st), (t / kStages) & 1, abort_flag, p, 641);
+        if (ok && t >= t_clean) {
+          mbar_arrive(bar(bLanded));
+          ok = wait_or_abort(bar(bClean), (t - t_clean) & 1, abort_flag, p, 643);
+        }
         if (!ok) break;
         tc_fence_after();
         const uint32_t a = base + st * kStageBytes;
@@ -874,7 +906,19 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
     using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
     const int r = threadIdx.x;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    if (wait_or_abort(bar(bOut), 0, abort_flag, p, 642)) {
+    bool ok = true;
+    for (int t = t_clean; ok && t < n_stages; ++t) {
+      const int st = t % kStages;
+      ok = wait_or_abort(bar(bLanded), (t - t_clean) & 1, abort_flag, p, 644);
+      if (!ok) break;
+      int keep = last_rows - (t & 1) * 64;   // rows of this stage that belong to the sequence
+      keep = keep < 0 ? 0 : keep;
+      zero_tile_rows(gbase + st * kStageBytes + 4 * kBox, keep, 64, 4, kBox, r, kBM);   // Q and dO: boxes 4..7 of the stage
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(bClean));
+    }
+    if (ok && wait_or_abort(bar(bOut), 0, abort_flag, p, 642)) {
       tc_fence_after();
       const int key = J * kBM + r;
       const bool valid = key < c.len;
@@ -931,7 +975,7 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
   const dim3 grid((unsigned)item_blocks(p, 1)), grid_pairs((unsigned)item_blocks(p, 2));
   if (!p.skip_dq) {
     auto kernel = tc_bwd_dq2_kernel<kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq2::kSmem);
+    e = allow_dynamic_smem(reinterpret_cast<const void *>(kernel), dq2::kSmem);
     if (e != cudaSuccess) return e;
     CUtensorMap mk64, mv64;   // 64-row boxes: the kernel streams 64-key sub-tiles
     if ((e = make_tile_map(&mk64, p.k, p, dtype, 64)) != cudaSuccess) return e;
@@ -945,7 +989,7 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
   }
   if (!p.skip_dkv && p.az != nullptr) {
     auto kernel = tc_bwd_dkv5_kernel<kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv5::kSmem);
+    e = allow_dynamic_smem(reinterpret_cast<const void *>(kernel), dkv5::kSmem);
     if (e != cudaSuccess) return e;
     CUtensorMap maz, mq64, mg64, mdk, mdv;
     if ((e = make_az_map(&maz, p, dtype)) != cudaSuccess) return e;
@@ -957,7 +1001,7 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   } else if (!p.skip_dkv) {
     auto kernel = tc_bwd_dkv4_kernel<kFp16>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv4::kSmem);
+    e = allow_dynamic_smem(reinterpret_cast<const void *>(kernel), dkv4::kSmem);
     if (e != cudaSuccess) return e;
     CUtensorMap mdk, mdv;   // stores: one 64-key strip at a time
     if ((e = make_tile_map(&mdk, p.dk, p, dtype, 64)) != cudaSuccess) return e;

@@ -30,6 +30,22 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return false;
 }
 
+// Zero-fills rows [row0, box_rows) of `boxes` consecutive [box_rows x 64] 16-bit boxes in shared memory (128-byte
+// rows; the 128-byte swizzle only permutes the 16-byte chunks inside a row, so whole rows are plain byte ranges).
+// The tensor maps cover the whole tokens axis, so a box that reaches past the end of its sequence holds the next
+// sequence's rows or whatever lies behind the last one.  Wherever such rows are an MMA operand whose partner is an
+// exact zero (V under P = 0, K under dz = 0, Q and dO under zero rows of dz and A) they are cleared first: 0 x NaN and
+// 0 x Inf are NaN.  Called by `nthreads` threads with indices `tid`; the caller fences (generic -> async proxy)
+// before it signals the MMA issuer.
+__device__ __forceinline__ void zero_tile_rows(uint8_t *tile, int row0, int box_rows, int boxes, int box_bytes, int tid,
+                                               int nthreads) {
+  const int chunks = (box_rows - row0) * 8;   // 16-byte chunks per box
+  for (int i = tid; i < chunks * boxes; i += nthreads) {
+    const int b = i / chunks, c = i - b * chunks;
+    *reinterpret_cast<uint4 *>(tile + b * box_bytes + row0 * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 template <bool kFp16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (kFp16) {
@@ -220,6 +236,8 @@ __device__ __forceinline__ void mma_mnmajor_mnmajor(uint32_t d_tmem, uint32_t a_
 
 // host: 4-D TMA map (head_dim, tokens, heads, batch), [64 x 128 x 1 x 1] box, 128-byte swizzle, zero fill
 cudaError_t make_tile_map(CUtensorMap *map, const TensorRef &t, const KParams &p, int dtype, int box_rows = kBM);
+// host: cudaFuncSetAttribute(MaxDynamicSharedMemorySize), issued once per kernel and device
+cudaError_t allow_dynamic_smem(const void *kernel, int bytes);
 // host: 4-D TMA map of the stored A / dz tiles, (keys 128, pairs * 128 query rows, {A, dz}, heads), [64 x 64 x 1 x 1] box
 cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype, int box_rows = 64);
 

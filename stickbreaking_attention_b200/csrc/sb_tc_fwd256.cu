@@ -308,7 +308,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float scale2 = p.scale * kLog2e;
     const int ac = p.attend_current;
-    int U = 0;
+    int U = 0, S = 0;   // this tile's steps and the K/V stages of the earlier items
     bool ok = true;
     Fwd256Item w_next;
     bool have = fwd256_item(p, 0, w);
@@ -335,6 +335,14 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc_fence_after();
         const uint32_t ts = tmem + wg * 128 + buf * 64 + lane_off;
         uint8_t *tile_p = gP + (wg * 2 + buf) * kPBytes;
+        // the sequence ends inside this sub-tile: the V rows behind its end are not this sequence's (see zero_tile_rows);
+        // their P columns are exact zeros, so the rows are cleared before this step's P V MMA is released
+        const int tail_rows = w.c.len - s * kBN;
+        if (tail_rows < kBN) {
+          uint8_t *v_tile = gbase + (sKV - base) + ((S + t0 + u) % kStages) * kStageBytes + kKvTileBytes;
+          zero_tile_rows(v_tile, tail_rows, kBN, kBoxes, kKvBoxBytes, r, kBM);
+          fence_proxy_async_smem();
+        }
         float R = ex2(-(float)run);
         float logsum = 0.f;
         // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
@@ -391,6 +399,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (lane == 0) mbar_arrive(bar(bOFree + wg));
       if ((threadIdx.x & 127) == 0) trace_event(p, 2 + wg, tr_cur, 46 + wg, it);
       U += my_steps;
+      S += w.n_steps;
       w = w_next;
       have = have_next;
     }
@@ -417,7 +426,7 @@ static cudaError_t launch_t(const KParams &p, int dtype, cudaStream_t s) {
   const dim3 grid((unsigned)(blocks < sms ? blocks : sms));   // one resident block per SM
   auto kernel = tc_fwd256_kernel<D, kFp16>;
   constexpr int smem = fwd256::Cfg<D>::kSmem;
-  if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+  if ((e = allow_dynamic_smem(reinterpret_cast<const void *>(kernel), smem)) != cudaSuccess) return e;
   kernel<<<grid, fwd256::kThreads, smem, s>>>(mq, mk, mv, mo, p);
   return cudaGetLastError();
 }

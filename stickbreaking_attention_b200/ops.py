@@ -18,6 +18,7 @@ Differences from the reference launchers, all on purpose:
 from __future__ import annotations
 
 import contextlib
+import threading
 from typing import Optional
 
 import torch
@@ -26,37 +27,60 @@ from . import _cabi
 
 NAMESPACE = "stickbreaking_attention_b200"
 
-_state = {"force_simt": False, "bwd_recompute": False, "launches": 0}
+class _Switches(threading.local):
+    """Per-thread switches (a trainer may drive several devices from several threads)."""
+    force_simt = False
+    bwd_recompute = False
+
+
+_state = _Switches()
+_launches = [0]   # process-wide: the backward's launches happen on autograd's thread
 _status_words: dict[int, torch.Tensor] = {}
 
 
 @contextlib.contextmanager
 def force_simt(enabled: bool = True):
-    """Within the block, bf16/fp16 calls run the CUDA-core kernels too (a cross-check in tests)."""
-    old = _state["force_simt"]
-    _state["force_simt"] = enabled
+    """Within the block (calling thread only), bf16/fp16 calls run the CUDA-core kernels too (a cross-check in tests)."""
+    old = _state.force_simt
+    _state.force_simt = enabled
     try:
         yield
     finally:
-        _state["force_simt"] = old
+        _state.force_simt = old
 
 
 @contextlib.contextmanager
 def small_backward_workspace(enabled: bool = True):
-    """Within the block the backward keeps its workspace small: the dK/dV kernel recomputes the attention tiles from
-    boundary values (a few KiB per tile pair) instead of reading the 64 KiB per pair the dQ kernel would store for it
-    (``SB_FLAG_BWD_RECOMPUTE``).  Slower, same results to rounding."""
-    old = _state["bwd_recompute"]
-    _state["bwd_recompute"] = enabled
+    """Within the block (calling thread only) the backward keeps its workspace small: the dK/dV kernel recomputes the
+    attention tiles from boundary values (a few KiB per tile pair) instead of reading the 64 KiB per pair the dQ kernel
+    would store for it (``SB_FLAG_BWD_RECOMPUTE``).  Slower, same results to rounding."""
+    old = _state.bwd_recompute
+    _state.bwd_recompute = enabled
     try:
         yield
     finally:
-        _state["bwd_recompute"] = old
+        _state.bwd_recompute = old
+
+
+def switch_flags() -> int:
+    """The calling thread's switches as C-ABI flag bits.  The autograd functions read them in their forward and hand
+    them to their backward: autograd runs the backward on a thread of its own, which does not see the caller's."""
+    return (_cabi.SB_FLAG_FORCE_SIMT if _state.force_simt else 0) | \
+           (_cabi.SB_FLAG_BWD_RECOMPUTE if _state.bwd_recompute else 0)
 
 
 def kernel_launches() -> int:
-    """Total kernel launches enqueued by this module since import (for benchmark accounting)."""
-    return _state["launches"]
+    """Total kernel launches enqueued through this module since import (for benchmark accounting)."""
+    return _launches[0]
+
+
+def set_backward_scratch_budget(nbytes: int) -> int:
+    """Process-wide upper bound on the scratch one chunk of heads of the backward may take (default 8 GiB); returns
+    the previous bound.  The backward stores 64 KiB per (query tile, key tile) pair and head for its dK/dV kernel and
+    works through the heads in chunks that fit the bound; a call whose single head does not fit recomputes the tiles
+    instead (slower, O(tokens) scratch).  Raising the bound on a GPU with memory to spare lets long sequences take the
+    stored-tiles kernels; lowering it bounds the transient allocation of every backward call."""
+    return int(_cabi.load().sb_set_backward_scratch_budget(int(nbytes)))
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -96,7 +120,7 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 
 
 def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero,
-          fuse_rem_v=False):
+          fuse_rem_v=False, switches=None):
     _require(q.is_cuda, "stick-breaking attention runs on a CUDA device only (no CPU path)")
     _require(q.dtype in _cabi.SB_DTYPE, f"unsupported dtype {q.dtype}")
     _require(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype")
@@ -120,8 +144,7 @@ def _fill(prm, *, fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_c
     prm.max_seqlen = 0 if max_seqlens is None else int(max_seqlens)
     prm.attend_current = int(bool(attend_current))
     prm.logit_scale = float(logit_scale)
-    prm.flags = (_cabi.SB_FLAG_FORCE_SIMT if _state["force_simt"] else 0) | \
-                (_cabi.SB_FLAG_BWD_RECOMPUTE if _state["bwd_recompute"] else 0) | \
+    prm.flags = (switch_flags() if switches is None else switches) | \
                 (_cabi.SB_FLAG_CHECK_LEADING_ZERO if leading_zero else 0) | \
                 (_cabi.SB_FLAG_FUSE_REM_V if fuse_rem_v else 0)
     prm.q = _cabi.tensor_arg(q, fixed)
@@ -139,30 +162,40 @@ def _run(backward: bool, prm, device):
     prm.workspace_bytes = workspace.numel()
     prm.status = _status_word(device).data_ptr()
     stream = torch.cuda.current_stream(device).cuda_stream
-    with torch.cuda.device(device):
-        rc = (lib.sb_bwd if backward else lib.sb_fwd)(prm, stream)
+    fn = lib.sb_bwd if backward else lib.sb_fwd
+    if device.index is None or device.index == torch.cuda.current_device():
+        rc = fn(prm, stream)
+    else:
+        with torch.cuda.device(device):
+            rc = fn(prm, stream)
     _cabi.check_call(lib, rc, "sb_bwd" if backward else "sb_fwd")
-    _state["launches"] += lib.sb_last_launch_count()
+    _launches[0] += lib.sb_last_launch_count()
     # the caching allocator keeps `workspace` alive until the stream has passed this point
     return workspace
 
 
 def _fwd_impl(fixed, q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero,
-              o, rem, log_rem, fuse_rem_v=False):
+              o, rem, log_rem, fuse_rem_v=False, attn=None):
     prm = _cabi.SbParams()
     _fill(prm, fixed=fixed, q=q, k=k, v=v, cu_seqlens=cu_seqlens, max_seqlens=max_seqlens,
           logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero, fuse_rem_v=fuse_rem_v)
     prm.o = _cabi.tensor_arg(o, fixed)
     prm.rem = rem.data_ptr()
     prm.log_rem = log_rem.data_ptr()
+    if attn is not None:
+        _require(attn.dtype == torch.float32 and attn.is_contiguous() and attn.shape[:-1] == q.shape[:-1],
+                 "the attention-weights buffer must be contiguous fp32 of shape (*q.shape[:-1], columns)")
+        prm.attn_weights = attn.data_ptr()
+        prm.attn_cols = attn.shape[-1]
     _run(False, prm, q.device)
 
 
 def _bwd_impl(fixed, do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current,
-              leading_zero, dq, dk, dv, fuse_rem_v=False):
+              leading_zero, dq, dk, dv, fuse_rem_v=False, switches=None):
     prm = _cabi.SbParams()
     _fill(prm, fixed=fixed, q=q, k=k, v=v, cu_seqlens=cu_seqlens, max_seqlens=max_seqlens,
-          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero, fuse_rem_v=fuse_rem_v)
+          logit_scale=logit_scale, attend_current=attend_current, leading_zero=leading_zero, fuse_rem_v=fuse_rem_v,
+          switches=switches)
     prm.log_rem = log_rem.data_ptr()
     prm.d_o = _cabi.tensor_arg(do, fixed)
     prm.d_rem = dr.data_ptr() if dr is not None else None
@@ -230,8 +263,8 @@ def _(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zer
 @torch.library.custom_op(f"{NAMESPACE}::bwd", mutates_args=(), device_types="cuda")
 def _op_bwd(do: torch.Tensor, dr: Optional[torch.Tensor], q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
             cu_seqlens: Optional[torch.Tensor], max_seqlens: int, log_rem: torch.Tensor, logit_scale: float,
-            attend_current: bool, leading_zero: bool,
-            fuse_rem_v: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+            attend_current: bool, leading_zero: bool, fuse_rem_v: bool,
+            switches: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     fixed = cu_seqlens is None
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     ends = None if fixed else _strip(cu_seqlens, leading_zero)
@@ -239,12 +272,13 @@ def _op_bwd(do: torch.Tensor, dr: Optional[torch.Tensor], q: torch.Tensor, k: to
         dr = torch.zeros(q.shape[:-1], dtype=q.dtype, device=q.device)
     _bwd_impl(fixed, _tma_ready(do.to(q.dtype)), None if dr is None else dr.to(q.dtype).contiguous(), _tma_ready(q),
               _tma_ready(k), _tma_ready(v), ends, max_seqlens if max_seqlens > 0 else None, log_rem, logit_scale,
-              attend_current, leading_zero and not fixed, dq, dk, dv, fuse_rem_v=fuse_rem_v)
+              attend_current, leading_zero and not fixed, dq, dk, dv, fuse_rem_v=fuse_rem_v, switches=switches)
     return dq, dk, dv
 
 
 @_op_bwd.register_fake
-def _(do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current, leading_zero, fuse_rem_v):
+def _(do, dr, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current, leading_zero, fuse_rem_v,
+      switches):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
@@ -252,6 +286,7 @@ def _fwd_setup_context(ctx, inputs, output):
     q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current, leading_zero, fuse_rem_v = inputs
     ctx.save_for_backward(q, k, v, output[2], cu_seqlens)
     ctx.args = (max_seqlens, logit_scale, attend_current, leading_zero, fuse_rem_v)
+    ctx.switches = switch_flags()
 
 
 def _fwd_backward(ctx, do, drem, dlog_rem):
@@ -260,7 +295,7 @@ def _fwd_backward(ctx, do, drem, dlog_rem):
     if do is None:
         do = torch.zeros_like(q)
     dq, dk, dv = _op_bwd(do, drem, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current,
-                         leading_zero, fuse_rem_v)
+                         leading_zero, fuse_rem_v, ctx.switches)
     return dq, dk, dv, None, None, None, None, None, None
 
 
@@ -286,14 +321,25 @@ def _strip(cu_seqlens, leading_zero):
 
 
 def varlen_fwd(q, k, v, cu_seqlens, max_seqlens: Optional[int], logit_scale: float,
-               attend_current: bool = False, leading_zero: bool = False):
+               attend_current: bool = False, leading_zero: bool = False, return_attention: bool = False):
     """Packed forward.  ``cu_seqlens`` holds sequence ends, preceded by a 0 iff ``leading_zero``.
-    Returns ``(o, rem, log_rem)`` like the reference returns ``(o, rem, neg_log_acc)``."""
+    Returns ``(o, rem, log_rem)`` like the reference returns ``(o, rem, neg_log_acc)``.
+
+    ``return_attention=True`` (``sb_varlen_fwd.py:413-449``, where the reference marks the output TODO) also returns
+    ``W``, fp32 ``(heads, tokens, max_seqlens)``: row t holds the weights of token t over the keys of its own sequence,
+    indexed from the sequence start, zeros elsewhere.  A debugging aid: O(tokens * max_seqlens) memory, and the call
+    runs the CUDA-core kernels whatever the dtype."""
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     o = torch.empty_like(q)
     rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
     log_rem = torch.empty(q.shape[:-1], dtype=torch.float64, device=q.device)
     ends = _strip(cu_seqlens, leading_zero)
+    if return_attention:
+        cols = q.shape[-2] if max_seqlens is None else min(int(max_seqlens), q.shape[-2])
+        attn = torch.zeros((*q.shape[:-1], cols), dtype=torch.float32, device=q.device)
+        _fwd_impl(False, q, k, v, ends, max_seqlens, logit_scale, attend_current, leading_zero, o, rem, log_rem,
+                  attn=attn)
+        return o, rem, log_rem, attn
     if _compiling():
         _op_varlen_fwd(q, k, v, ends, 0 if max_seqlens is None else int(max_seqlens), float(logit_scale),
                        bool(attend_current), bool(leading_zero), o, rem, log_rem)
@@ -303,8 +349,9 @@ def varlen_fwd(q, k, v, cu_seqlens, max_seqlens: Optional[int], logit_scale: flo
 
 
 def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens: Optional[int], log_rem, logit_scale: float,
-               attend_current: bool = False, leading_zero: bool = False):
-    """Packed backward; returns ``(dq, dk, dv)`` in the dtype of the inputs."""
+               attend_current: bool = False, leading_zero: bool = False, switches: Optional[int] = None):
+    """Packed backward; returns ``(dq, dk, dv)`` in the dtype of the inputs.  ``switches``: the ``switch_flags()`` of
+    the forward call (default: the calling thread's)."""
     q, k, v, do = _tma_ready(q), _tma_ready(k), _tma_ready(v), _tma_ready(do.to(q.dtype))
     dr = dr.to(q.dtype).contiguous()
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -314,16 +361,21 @@ def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens: Optional[int], log_rem,
                        float(logit_scale), bool(attend_current), bool(leading_zero), dq, dk, dv)
     else:
         _bwd_impl(False, do, dr, q, k, v, ends, max_seqlens, log_rem, logit_scale, attend_current,
-                  leading_zero, dq, dk, dv)
+                  leading_zero, dq, dk, dv, switches=switches)
     return dq, dk, dv
 
 
-def attn_fwd(q, k, v, logit_scale: float, attend_current: bool = False):
-    """Fixed-length ``(B,H,T,d)`` forward; returns ``(o, rem, log_rem)``."""
+def attn_fwd(q, k, v, logit_scale: float, attend_current: bool = False, return_attention: bool = False):
+    """Fixed-length ``(B,H,T,d)`` forward; returns ``(o, rem, log_rem)``, and with ``return_attention=True`` also the
+    fp32 weights ``W (B,H,T,T)`` (see ``varlen_fwd``)."""
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     o = torch.empty_like(q)
     rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
     log_rem = torch.empty(q.shape[:-1], dtype=torch.float64, device=q.device)
+    if return_attention:
+        attn = torch.zeros((*q.shape[:-1], q.shape[-2]), dtype=torch.float32, device=q.device)
+        _fwd_impl(True, q, k, v, None, None, logit_scale, attend_current, False, o, rem, log_rem, attn=attn)
+        return o, rem, log_rem, attn
     if _compiling():
         _op_attn_fwd(q, k, v, float(logit_scale), bool(attend_current), o, rem, log_rem)
     else:
@@ -331,7 +383,8 @@ def attn_fwd(q, k, v, logit_scale: float, attend_current: bool = False):
     return o, rem, log_rem
 
 
-def attn_bwd(do, dr, q, k, v, log_rem, logit_scale: float, attend_current: bool = False):
+def attn_bwd(do, dr, q, k, v, log_rem, logit_scale: float, attend_current: bool = False,
+             switches: Optional[int] = None):
     """Fixed-length backward; returns ``(dq, dk, dv)`` in the dtype of the inputs (the reference
     forces dk and dv to bf16 here, ``sb_attn/sb_bwd.py:173-174``; this keeps the input dtype)."""
     q, k, v, do = _tma_ready(q), _tma_ready(k), _tma_ready(v), _tma_ready(do.to(q.dtype))
@@ -340,7 +393,8 @@ def attn_bwd(do, dr, q, k, v, log_rem, logit_scale: float, attend_current: bool 
     if _compiling():
         _op_attn_bwd(do, dr, q, k, v, log_rem, float(logit_scale), bool(attend_current), dq, dk, dv)
     else:
-        _bwd_impl(True, do, dr, q, k, v, None, None, log_rem, logit_scale, attend_current, False, dq, dk, dv)
+        _bwd_impl(True, do, dr, q, k, v, None, None, log_rem, logit_scale, attend_current, False, dq, dk, dv,
+                  switches=switches)
     return dq, dk, dv
 
 
@@ -360,7 +414,7 @@ def fused_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=Fals
 
 
 def fused_bwd(dout, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, attend_current=False,
-              leading_zero=False):
+              leading_zero=False, switches=None):
     """Backward of ``fused_fwd``'s ``out``: ``<d_out, v>`` goes into the gradient of rem and ``rem * d_out`` into dv
     inside the library; returns ``(dq, dk, dv)``."""
     fixed = cu_seqlens is None
@@ -368,7 +422,7 @@ def fused_bwd(dout, q, k, v, cu_seqlens, max_seqlens, log_rem, logit_scale, atte
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     ends = None if fixed else _strip(cu_seqlens, leading_zero)
     _bwd_impl(fixed, dout, None, q, k, v, ends, max_seqlens, log_rem, logit_scale, attend_current,
-              leading_zero and not fixed, dq, dk, dv, fuse_rem_v=True)
+              leading_zero and not fixed, dq, dk, dv, fuse_rem_v=True, switches=switches)
     return dq, dk, dv
 
 

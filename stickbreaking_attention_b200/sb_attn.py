@@ -20,13 +20,14 @@ class StickBreakingAttention(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, log_rem)
         ctx.logit_scale = inv_temp
         ctx.attend_current = attend_current
+        ctx.switches = ops.switch_flags()   # the backward runs on autograd's thread: it gets the caller's switches
         return o, rem
 
     @staticmethod
     def backward(ctx, do, drem):
         q, k, v, log_rem = ctx.saved_tensors
         dq, dk, dv = ops.attn_bwd(do, drem, q, k, v, log_rem, ctx.logit_scale,
-                                  attend_current=ctx.attend_current)
+                                  attend_current=ctx.attend_current, switches=ctx.switches)
         return dq, dk, dv, None, None
 
 
@@ -51,14 +52,15 @@ class StickBreakingAttentionFused(torch.autograd.Function):
     def forward(ctx, q, k, v, inv_temp, attend_current=False):
         out, _, log_rem = ops.fused_fwd(q, k, v, None, None, inv_temp, attend_current=attend_current)
         ctx.save_for_backward(q, k, v, log_rem)
-        ctx.args = (inv_temp, attend_current)
+        ctx.args = (inv_temp, attend_current, ops.switch_flags())
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, log_rem = ctx.saved_tensors
-        inv_temp, attend_current = ctx.args
-        dq, dk, dv = ops.fused_bwd(dout, q, k, v, None, None, log_rem, inv_temp, attend_current=attend_current)
+        inv_temp, attend_current, switches = ctx.args
+        dq, dk, dv = ops.fused_bwd(dout, q, k, v, None, None, log_rem, inv_temp, attend_current=attend_current,
+                                   switches=switches)
         return dq, dk, dv, None, None
 
 

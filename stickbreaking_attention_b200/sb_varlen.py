@@ -25,6 +25,7 @@ class StickBreakingAttention(torch.autograd.Function):
         ctx.max_seqlens = max_seqlens
         ctx.attend_current = attend_current
         ctx.leading_zero = leading_zero
+        ctx.switches = ops.switch_flags()   # the backward runs on autograd's thread: it gets the caller's switches
         return o, rem
 
     @staticmethod
@@ -32,7 +33,7 @@ class StickBreakingAttention(torch.autograd.Function):
         q, k, v, log_rem, cu_seqlens = ctx.saved_tensors
         dq, dk, dv = ops.varlen_bwd(do, drem, q, k, v, cu_seqlens, ctx.max_seqlens, log_rem,
                                     ctx.logit_scale, attend_current=ctx.attend_current,
-                                    leading_zero=ctx.leading_zero)
+                                    leading_zero=ctx.leading_zero, switches=ctx.switches)
         return dq, dk, dv, None, None, None, None, None
 
 
@@ -67,15 +68,15 @@ class StickBreakingAttentionFused(torch.autograd.Function):
         out, _, log_rem = ops.fused_fwd(q, k, v, cu_seqlens, max_seqlens, inv_temp,
                                         attend_current=attend_current, leading_zero=leading_zero)
         ctx.save_for_backward(q, k, v, log_rem, cu_seqlens)
-        ctx.args = (max_seqlens, inv_temp, attend_current, leading_zero)
+        ctx.args = (max_seqlens, inv_temp, attend_current, leading_zero, ops.switch_flags())
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, log_rem, cu_seqlens = ctx.saved_tensors
-        max_seqlens, inv_temp, attend_current, leading_zero = ctx.args
+        max_seqlens, inv_temp, attend_current, leading_zero, switches = ctx.args
         dq, dk, dv = ops.fused_bwd(dout, q, k, v, cu_seqlens, max_seqlens, log_rem, inv_temp,
-                                   attend_current=attend_current, leading_zero=leading_zero)
+                                   attend_current=attend_current, leading_zero=leading_zero, switches=switches)
         return dq, dk, dv, None, None, None, None, None
 
 

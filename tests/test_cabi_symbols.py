@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_symbols():
         assert hasattr(lib, name), name
     assert set(_cabi.EXPORTS) <= set(declared_symbols())
-    assert lib.sb_abi_version() == 1
+    assert lib.sb_abi_version() == _cabi.ABI_VERSION == 2
 
 
 def test_struct_layout_matches_header():
@@ -45,6 +45,28 @@ def test_struct_layout_matches_header():
     p.struct_bytes -= 8
     assert lib.sb_workspace_bytes(p, 0) == 2 ** 64 - 1
     assert b"struct_bytes" in lib.sb_last_error()
+
+
+def test_scratch_budget_changes_the_backward_workspace():
+    """sb_set_backward_scratch_budget is a host-side setting: a smaller budget gives a smaller backward workspace."""
+    from stickbreaking_attention_b200 import _cabi
+    lib = _cabi.load()
+    p = _cabi.SbParams()
+    p.struct_bytes = ctypes.sizeof(_cabi.SbParams)
+    p.dtype, p.batch, p.heads, p.head_dim, p.tokens = 1, 2, 8, 128, 2048
+    for name in ("q", "k", "v", "d_o", "dq", "dk", "dv"):     # plausible addresses and strides; never dereferenced
+        setattr(p, name, _cabi.SbTensor(4096, 8 * 2048 * 128, 2048 * 128, 128))
+    default = lib.sb_set_backward_scratch_budget(0)
+    assert default == 8 << 30
+    big = lib.sb_workspace_bytes(p, 1)
+    per_head = 2 * 136 * 65536                       # 2 batch elements x 136 tile pairs x 64 KiB
+    assert big >= 8 * per_head
+    assert lib.sb_set_backward_scratch_budget(3 * per_head) == default
+    assert lib.sb_workspace_bytes(p, 1) < 4 * per_head
+    assert lib.sb_set_backward_scratch_budget(default) == 3 * per_head
+    assert lib.sb_workspace_bytes(p, 1) == big
+    p.reserved = 1
+    assert lib.sb_workspace_bytes(p, 1) == 2 ** 64 - 1 and b"reserved" in lib.sb_last_error()
 
 
 def test_missing_library_fails_loudly(tmp_path):

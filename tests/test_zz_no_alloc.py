@@ -68,4 +68,15 @@ def test_static_scratch_rejects_what_does_not_fit(cuda_device):
     assert lib.sb_workspace_bytes(prm, 0) > _cabi.SB_STATIC_SCRATCH_BYTES
     rc = lib.sb_fwd_static_scratch(prm, torch.cuda.current_stream(cuda_device).cuda_stream)
     assert rc == 2 and b"scratch" in lib.sb_last_error()
+    # the same rule on the CUDA-core path (fp32), whose work items are 32 tokens: 600 sequences in 262144 tokens fit
+    # in bf16 (256-token items) and do not in fp32
+    lengths = torch.full((600,), 436, dtype=torch.int32)
+    cu = lengths.cumsum(0).to(torch.int32).to(cuda_device)
+    for dtype, fits in ((torch.bfloat16, True), (torch.float32, False)):
+        q = torch.zeros(1, 262144, 64, dtype=dtype, device=cuda_device)
+        prm, _ = _params(sb, q, q, q, cu, 436)
+        assert (lib.sb_workspace_bytes(prm, 0) <= _cabi.SB_STATIC_SCRATCH_BYTES) == fits
+        rc = lib.sb_fwd_static_scratch(prm, torch.cuda.current_stream(cuda_device).cuda_stream)
+        assert (rc == 0) == fits, lib.sb_last_error()
     torch.cuda.synchronize(cuda_device)
+    sb.check_status(cuda_device)
