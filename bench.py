@@ -11,17 +11,22 @@ GPU under torchrun) every rank runs its own batch of that shape: the path shards
 the algorithmic FLOPs divided by the slowest rank's device time.
 
 Printed by rank 0, one JSON line:
-  value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks
+  value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks; the K-step timed
+             loop is repeated (``timing.repeats``) and the median repetition is the one reported
   e2e        same metric through the public Python operator with pinned HOST buffers: the H2D copies of
              q, k, v, dO, dRem and the D2H copies of o, rem, dq, dk, dv are inside the timed region (every step
              copies all of them; the copies of neighbouring steps overlap the compute on separate streams)
   roofline   the dominant kernel against the measured dense bf16 tensor peak
-  cpu_baseline  the CPU oracle (a port of the reference's sb_ref) on a bounded sample, rank 0, N == 1
+  cpu_baseline  the reference's own sb_ref.stickbreaking on the host cores (from the reference installation under
+             baseline/_ref when it is there, else this repository's port of it), bounded sample, rank 0, N == 1
+  sharded    the long-context workload split by heads and the skewed packed workload split by sequences across the
+             N ranks (strong scaling: the total work is fixed), each plan with its slowest and mean rank time, and a
+             bitwise comparison of the gathered shards (NCCL, outside the timed region) with an unsharded run
 
 FLOP convention (causal): forward 2*L^2*d per head per sequence, backward 2.5x that.
 
-``--impl reference`` times the reference's CPU algorithm (the oracle port; the reference itself is a
-Python package that does not travel to the GPU box) on the host cores instead.
+``--impl reference`` times the reference's CPU implementation of the path on the host cores instead: every
+step runs the whole workload (all heads, all sequences, split per sequence as the reference's tests do).
 """
 from __future__ import annotations
 
@@ -41,9 +46,27 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
-# profiles/tc_kernels_c2_ncu.md (workload c2 only; other workloads report null)
-NCU_TRAFFIC_BYTES = {"c2": {"fwd": 495.8e6, "bwd_dq": 1462.0e6, "bwd_dkv": 1402.4e6}}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of this workload.  The figures belong
+# to the kernel sources whose digest is recorded with them: after any change to the kernels they are stale, and
+# `roofline.traffic` is reported as null until a new capture is entered here.
+NCU_TRAFFIC = {"kernel_sources_sha256_16": "", "bytes": {"c2": {"fwd": 495.8e6, "bwd_dq": 1462.0e6, "bwd_dkv": 1402.4e6}}}
+
+
+def kernel_sources_digest():
+    import hashlib
+    csrc = os.path.join(ROOT, "stickbreaking_attention_b200", "csrc")
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(csrc)):
+        if name.endswith((".cu", ".cuh")):
+            with open(os.path.join(csrc, name), "rb") as f:
+                h.update(name.encode() + b"\0" + f.read())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic(workload_name, kernel):
+    if NCU_TRAFFIC["kernel_sources_sha256_16"] != kernel_sources_digest():
+        return None
+    return NCU_TRAFFIC["bytes"].get(workload_name, {}).get(kernel)
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -129,7 +152,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.004)
 
     def __enter__(self):
         if self.nv is not None:
@@ -148,60 +171,123 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------
-# CPU arm: the oracle port of the reference's algorithm on the host cores
+# CPU arm: the reference's sb_ref.stickbreaking on the host cores
 # ---------------------------------------------------------------------------------------------------
-def cpu_sample(w, heads, seqs, reps):
-    """Times forward+backward of the oracle on `heads` heads x the first `seqs` sequences; returns
-    (best seconds, TFLOP/s under the causal convention, description)."""
-    from oracle import sb_oracle as O
+def load_reference_sb_ref():
+    """The reference's own sb_ref module, loaded by file path from its installation under baseline/_ref (a pure
+    torch file; nothing else of the reference is imported), or None when that installation is absent."""
+    import importlib.util
+    path = os.path.join(ROOT, "baseline", "_ref", "stickbreaking_attention", "sb_ref.py")
+    if not os.path.exists(path):
+        return None
+    spec = importlib.util.spec_from_file_location("_reference_sb_ref", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def use_all_host_threads():
     try:   # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except Exception:
         pass
+    return torch.get_num_threads()
+
+
+def cpu_inputs(w, heads, seqs):
     lengths = w["lengths"][:seqs]
     gen = torch.Generator().manual_seed(0)
     shape = (heads, sum(lengths), w["head_dim"])
     q, k, v = (w["std"] * torch.randn(shape, generator=gen) for _ in range(3))
     do = torch.randn(shape, generator=gen)
     drem = torch.randn(shape[:2], generator=gen)
+    return lengths, q, k, v, do, drem
+
+
+def cpu_step(ref, w, lengths, q, k, v, do, drem):
+    """One forward + backward of the workload slice on the CPU, fp32.  With the reference module: its dense function
+    per sequence with the mask and cumulative-weight matrices its tests build (tests/test_varlen.py:10-27 of the
+    reference), gradients by autograd for upstream gradients of both outputs.  Sequences too long for the dense
+    L x L matrices, or no reference installation: this repository's port (row-blocked where needed)."""
+    from oracle import sb_oracle as O
     cu = torch.tensor(lengths).cumsum(0)
-    fn = O.varlen_dense_grads if max(lengths) <= 4096 else O.varlen_rowblocked_grads
-    best = float("inf")
+    if ref is None or max(lengths) > 4096:
+        fn = O.varlen_dense_grads if max(lengths) <= 4096 else O.varlen_rowblocked_grads
+        fn(q, k, v, cu, do, drem)
+        return "port"
+    start = 0
+    for n in lengths:
+        sl = slice(start, start + n)
+        qs, ks, vs = (t[None, :, sl].detach().clone().requires_grad_(True) for t in (q, k, v))
+        cm = torch.ones(n, n).tril(-1)
+        mask = torch.ones(n, n).triu(0).bool()
+        o, rem = ref.stickbreaking(qs, ks, vs, mask, cm)
+        torch.autograd.grad((o, rem), (qs, ks, vs), (do[None, :, sl], drem[None, :, sl]))
+        start += n
+    return "reference"
+
+
+def cpu_sample(w, heads, seqs, reps):
+    """Times `reps` CPU steps over `heads` heads x the first `seqs` sequences; returns
+    (best seconds, TFLOP/s under the causal convention, description, kind)."""
+    ref = load_reference_sb_ref()
+    use_all_host_threads()
+    lengths, q, k, v, do, drem = cpu_inputs(w, heads, seqs)
+    best, kind = float("inf"), "port"
     for _ in range(reps):
         t0 = time.perf_counter()
-        fn(q, k, v, cu, do, drem)
+        kind = cpu_step(ref, w, lengths, q, k, v, do, drem)
         best = min(best, time.perf_counter() - t0)
     fl = 7.0 * w["head_dim"] * heads * float(sum(n * n for n in lengths))
-    desc = (f"{heads} heads x first {seqs} sequence(s) ({sum(lengths)} tokens) of the workload, fp32, "
-            f"forward + autograd backward, best of {reps}")
-    return best, fl / best / 1e12, desc
+    whole = heads == w["heads"] and seqs >= len(w["lengths"])
+    desc = (("the whole workload" if whole else
+             f"{heads} of {w['heads']} heads x the first {len(lengths)} of {len(w['lengths'])} sequence(s)")
+            + f" ({sum(lengths)} tokens), fp32, forward + autograd backward, best of {reps}")
+    return best, fl / best / 1e12, desc, kind
 
 
 def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    heads, seqs = min(4, w["heads"]), 1
-    cpu_sample(w, 1, 1, 1)            # sets the thread count; also warms the allocator
-    threads = torch.get_num_threads()
-    times = []
-    tfl = 0.0
-    desc = ""
-    for i in range(args.warmup + args.steps):
-        sec, tfl_i, desc = cpu_sample(w, heads, seqs, 1)
+    ref = load_reference_sb_ref()
+    threads = use_all_host_threads()
+    heads, seqs = w["heads"], len(w["lengths"])      # every step is the whole workload ...
+    if max(w["lengths"]) > 4096:
+        seqs = 1
+    lengths, q, k, v, do, drem = cpu_inputs(w, heads, seqs)
+    times, kind = [], "port"
+    total = args.warmup + args.steps
+    i = 0
+    while i < total:
+        t0 = time.perf_counter()
+        kind = cpu_step(ref, w, lengths, q, k, v, do, drem)
+        dt = time.perf_counter() - t0
+        # ... unless the first step shows that W + K such steps would not end within the time allowed: then the
+        # steps go on with as many heads as fit it (the per-head work is identical; the sample line says what ran)
+        if i == 0 and heads > 1 and dt * total > args.reference_budget_s:
+            heads = max(1, int(heads * args.reference_budget_s / (dt * total)))
+            lengths, q, k, v, do, drem = cpu_inputs(w, heads, seqs)
+            continue
         if i >= args.warmup:
-            times.append(sec)
-            tfl = max(tfl, tfl_i)
+            times.append(dt)
+        i += 1
     mean = sum(times) / len(times)
-    fl = 7.0 * w["head_dim"] * heads * float(sum(n * n for n in w["lengths"][:seqs]))
+    fl = 7.0 * w["head_dim"] * heads * float(sum(n * n for n in lengths))
     value = fl / mean / 1e12
+    whole = heads == w["heads"] and seqs == len(w["lengths"])
+    desc = (("every step is the whole workload: " if whole else "every step is a part of the workload: ")
+            + f"{heads} of {w['heads']} heads x {seqs} of {len(w['lengths'])} sequence(s), {sum(lengths)} tokens, fp32, "
+            f"forward + autograd backward, split per sequence")
     line = {
         "impl": "reference", "metric": "sb_attn_varlen fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["label"], "sample_per_step": desc, "host_cores": os.cpu_count(),
-                   "torch_threads": threads},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc},
+        "config": {"workload": w["label"], "name": args.workload, "sample_per_step": desc,
+                   "host_cores": os.cpu_count(), "torch_threads": threads,
+                   "function": ("stickbreaking_attention/sb_ref.py:stickbreaking of the installed reference"
+                                if kind == "reference" else "this repository's port of sb_ref.stickbreaking")},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": desc},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -353,29 +439,50 @@ def run_gpu_arm(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(step, steps, warmup):
+    def timed(step, steps, warmup, repeats):
+        """`repeats` repetitions of the `steps`-long loop, each bracketed by a barrier and a device synchronisation and
+        timed with CUDA events; every repetition's time is the max over ranks.  Returns per-step ms of all
+        repetitions, the launches of one repetition and the clocks seen under load."""
         for _ in range(warmup):
             step()
         barrier()
-        launches0 = sb.kernel_launches()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        per_step, launches = [], 0
         with ClockSampler(local_rank) as clocks:
-            start.record()
-            for _ in range(steps):
-                step()
-            stop.record()
-            barrier()
-        ms = start.elapsed_time(stop)
+            for _ in range(repeats):
+                barrier()
+                launches0 = sb.kernel_launches()
+                start.record()
+                for _ in range(steps):
+                    step()
+                stop.record()
+                barrier()
+                launches = sb.kernel_launches() - launches0
+                per_step.append(start.elapsed_time(stop) / steps)
         if distributed:
-            t = torch.tensor([ms], device=device)
+            t = torch.tensor(per_step, device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps, sb.kernel_launches() - launches0, clocks.summary()
+            per_step = t.tolist()
+        return per_step, launches, clocks.summary()
 
-    ms_step, launches, clocks = timed(step_resident, args.steps, max(args.warmup, 3))
+    def host_time_us(step, calls=20):
+        """Host time of one un-synchronised forward + backward call: what the Python and C layers cost per step."""
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            step()
+        dt = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        return dt / calls * 1e6
+
+    repeats = max(1, args.repeats)
+    ms_reps, launches, clocks = timed(step_resident, args.steps, max(args.warmup, 3), repeats)
+    ms_step = statistics.median(ms_reps)
     sb.check_status(device)
+    host_us = host_time_us(step_resident)
     e2e_steps = max(3, min(args.steps, 20))
-    ms_e2e, _, _ = timed(step_e2e, e2e_steps, 3)
+    e2e_reps, _, _ = timed(step_e2e, e2e_steps, 3, min(repeats, 3))
+    ms_e2e = statistics.median(e2e_reps)
 
     fl = flops_of(w, mode)
     value = fl * world / (ms_step * 1e-3) / 1e12
@@ -393,7 +500,7 @@ def run_gpu_arm(args, w):
         achieved = kernels[top]["tflops"]
         roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                    "traffic": NCU_TRAFFIC_BYTES.get(args.workload, {}).get(top),
+                    "traffic": ncu_traffic(args.workload, top),
                     "peak_source": f"{peak_kind} dense bf16 (burst)", "kernels": kernels,
                     "step_frac_of_peak": value / world / peaks["bf16_tflops"],
                     "kernel_path": "tcgen05" if path == 1 else "cuda-core"}
@@ -409,9 +516,10 @@ def run_gpu_arm(args, w):
                                  "algorithmic_bytes": alg_bytes})
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            heads = min(8, w["heads"])
-            sec, tfl, desc = cpu_sample(w, heads, 1, 3)
-            cpu = {"value": tfl, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            heads = min(4, w["heads"])
+            seqs = len(w["lengths"]) if max(w["lengths"]) <= 4096 else 1
+            sec, tfl, desc, kind = cpu_sample(w, heads, seqs, 2)
+            cpu = {"value": tfl, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
                    "sample": desc, "seconds": sec, "host_cores": os.cpu_count()}
         line = {
             "metric": "sb_attn_varlen fwd+bwd TFLOP/s" if not fwd_only else "sb_attn_varlen fwd TFLOP/s",
@@ -424,19 +532,156 @@ def run_gpu_arm(args, w):
                        "l2": "q,k,v,dO and the outputs of one step exceed the 126 MB L2; no flush between steps",
                        "flop_convention": "causal: fwd 2*L^2*d per head per sequence, bwd 2.5x"},
             "tokens_per_s": sum(w["lengths"]) * world / (ms_step * 1e-3),
+            "timing": {"repeats": repeats, "ms_per_step_median": ms_step, "ms_per_step_min": min(ms_reps),
+                       "ms_per_step_max": max(ms_reps), "host_us_per_step": host_us,
+                       "note": "each repetition: barrier, K steps between CUDA events, barrier; max over ranks; "
+                               "value uses the median repetition; host_us_per_step is the wall time the Python and C "
+                               "layers take to enqueue one forward + backward (rank 0, no synchronisation)"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e, "steps": e2e_steps,
+                    "ms_per_step": ms_e2e, "steps": e2e_steps, "repeats": len(e2e_reps),
+                    "pinned_gb_per_s_per_rank": (h2d + d2h) / (ms_e2e * 1e-3) / 1e9,
                     "overlap": "h2d of step i+1 and d2h of step i-1 run on their own streams while step i computes"},
-            "gpu_launches": launches,
+            "gpu_launches": launches * repeats,
+            "gpu_launches_per_repetition": launches,
             "clocks": clocks,
             "roofline": roofline,
             "cpu_baseline": cpu,
         }
+    if not args.no_sharded and args.workload == "c2":
+        sharded = run_sharded(sb, device, rank, world, dist if distributed else None)
+        if line is not None:
+            line["sharded"] = sharded
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# the same total work split across the ranks (strong scaling); no collective inside any timed region
+# ---------------------------------------------------------------------------------------------------
+def run_sharded(sb, device, rank, world, dist, steps=3):
+    """Long-context workload (one 131072-token sequence, 16 heads) split by heads, and the skewed packed workload
+    (65536 tokens in lognormal-length sequences, 32 heads) split by sequences under three plans: contiguous
+    token-balanced runs, contiguous runs balanced by sum of L^2, and longest-first assignment of whole sequences.
+    Every rank builds the full inputs from the same seed on its own GPU, keeps its shard and runs the ordinary
+    operator on it.  Times: CUDA events per rank, max and mean over ranks.  Afterwards, outside any timed region, the
+    shards' results are gathered over NCCL and rank 0 compares them bitwise with an unsharded run."""
+    from stickbreaking_attention_b200 import shard
+
+    def full_inputs(w, seed):
+        gen = torch.Generator(device=device).manual_seed(seed)
+        T = sum(w["lengths"])
+        shape = (w["heads"], T, w["head_dim"])
+        t = {}
+        for name in ("q", "k", "v"):
+            t[name] = (w["std"] * torch.randn(shape, generator=gen, device=device)).to(torch.bfloat16)
+        t["do"] = torch.randn(shape, generator=gen, device=device).to(torch.bfloat16)
+        t["drem"] = torch.randn(shape[:2], generator=gen, device=device).to(torch.bfloat16)
+        return t
+
+    def run_op(t, lengths, n_steps):
+        """(outputs of the last step, ms per step) of forward + backward over the packed tensors in t."""
+        if not lengths or t["q"].shape[0] == 0:
+            return None, 0.0
+        cu = torch.tensor(lengths, dtype=torch.int32).cumsum(0).to(torch.int32).to(device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        outs = None
+        for i in range(n_steps + 2):          # two warm-up steps
+            if i == 2:
+                torch.cuda.synchronize()
+                start.record()
+            q, k, v = (t[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
+            o, rem = sb.sb_attn_varlen(q, k, v, cu, max(lengths), zero_start=False)
+            dq, dk, dv = torch.autograd.grad((o, rem), (q, k, v), (t["do"], t["drem"]))
+            outs = {"o": o.detach(), "rem": rem.detach(), "dq": dq, "dk": dk, "dv": dv}
+        stop.record()
+        torch.cuda.synchronize()
+        return outs, start.elapsed_time(stop) / n_steps
+
+    def rank_times(ms):
+        if dist is None:
+            return [ms]
+        t = torch.zeros(world, device=device, dtype=torch.float64)
+        t[rank] = ms
+        dist.all_reduce(t)
+        return t.tolist()
+
+    def summarise(w, times, extra):
+        slow = max(times)
+        fl = flops_of(w, "fwd_bwd")
+        out = {"ms_max": slow, "ms_mean": sum(times) / len(times), "ms_per_rank": times,
+               "tokens_per_s": sum(w["lengths"]) / (slow * 1e-3), "tflops": fl / (slow * 1e-3) / 1e12}
+        out.update(extra)
+        return out
+
+    result = {"scaling": "strong", "ranks": world, "steps": steps}
+
+    # ---- one long sequence, split by heads
+    w4 = workload("c4")
+    full = full_inputs(w4, 4242)
+    h0, h1 = shard.head_range(w4["heads"], world, rank)
+    mine = {n: x[h0:h1] for n, x in full.items()}
+    if dist is not None:
+        dist.barrier()
+    outs, ms = run_op(mine, w4["lengths"], steps)
+    times = rank_times(ms)
+    verify = None
+    if dist is not None:
+        gathered = {n: shard.all_gather_heads(x, w4["heads"]) for n, x in outs.items()}
+        if rank == 0:
+            pick = [0, w4["heads"] - 1]
+            ref_outs, _ = run_op({n: x[pick].contiguous() for n, x in full.items()}, w4["lengths"], 1)
+            verify = all(torch.equal(gathered[n][pick], ref_outs[n]) for n in ref_outs)
+        del gathered
+    result["long_context_by_heads"] = summarise(
+        w4, times, {"workload": w4["label"], "heads_per_rank": h1 - h0, "plan": "shard.head_range",
+                    "gathered_equals_unsharded": verify})
+    del full, mine, outs
+    torch.cuda.empty_cache()
+
+    # ---- skewed packed batch, split by sequences
+    w3 = workload("c3")
+    lengths = w3["lengths"]
+    full = full_inputs(w3, 4343)
+    whole_outs = None
+    if dist is not None and rank == 0:
+        whole_outs, _ = run_op(full, lengths, 1)
+    plans = {
+        "contiguous_by_tokens": [list(range(a, b)) for a, b in shard.contiguous_segments(lengths, world, by="tokens")],
+        "contiguous_by_work": [list(range(a, b)) for a, b in shard.contiguous_segments(lengths, world, by="work")],
+        "lpt_by_work": shard.lpt_assignment(lengths, world, by="work"),
+    }
+    result["skewed_by_sequences"] = {"workload": w3["label"], "sequences": len(lengths),
+                                     "longest": max(lengths), "plans": {}}
+    for name, parts in plans.items():
+        seqs = parts[rank]
+        tensors, my_lengths, index = shard.slice_packed([full[n] for n in ("q", "k", "v", "do", "drem")], lengths, seqs)
+        mine = dict(zip(("q", "k", "v", "do", "drem"), (x.contiguous() for x in tensors)))
+        if dist is not None:
+            dist.barrier()
+        outs, ms = run_op(mine, my_lengths, steps)
+        times = rank_times(ms)
+        verify = None
+        if dist is not None:
+            ok = True
+            for n in ("o", "rem", "dq", "dk", "dv"):
+                # a rank whose plan gave it no sequence still takes part in the gather, with zero tokens
+                local = outs[n] if outs is not None else full["drem" if n == "rem" else "q"][:, :0]
+                gathered = shard.all_gather_tokens(local, index, sum(lengths))
+                if rank == 0:
+                    ok = ok and torch.equal(gathered, whole_outs[n])
+                del gathered
+            verify = ok if rank == 0 else None
+        result["skewed_by_sequences"]["plans"][name] = summarise(
+            w3, times, {"imbalance_tokens": shard.imbalance(lengths, parts, by="tokens"),
+                        "imbalance_work": shard.imbalance(lengths, parts, by="work"),
+                        "sequences_per_rank": [len(p) for p in parts], "gathered_equals_unsharded": verify})
+        del mine, outs
+    del full, whole_outs
+    torch.cuda.empty_cache()
+    return result
 
 
 def main():
@@ -447,6 +692,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sharded workloads (profiler runs)")
+    ap.add_argument("--repeats", type=int, default=10, help="repetitions of the timed K-step loop")
+    ap.add_argument("--reference-budget-s", type=float, default=1200.0,
+                    help="--impl reference: wall-clock allowance for the W + K steps; the whole workload runs per step "
+                         "unless the first step shows that it would not fit")
     ap.add_argument("--small-workspace", action="store_true",
                     help="backward recomputes the attention tiles in the dK/dV kernel instead of storing them")
     args = ap.parse_args()
