@@ -637,7 +637,26 @@ def run_sharded(sb, device, rank, world, dist, steps=3):
         del gathered
     result["long_context_by_heads"] = summarise(
         w4, times, {"workload": w4["label"], "heads_per_rank": h1 - h0, "plan": "shard.head_range",
-                    "gathered_equals_unsharded": verify})
+                    "backward": "recomputing dK/dV kernel (one head's stored tiles, 34 GB, exceed the default 8 GiB "
+                                "scratch budget)", "gathered_equals_unsharded": verify})
+    # the same split with the backward's scratch budget raised to 40 GiB, where the GPU has the memory to spare: one
+    # head's tiles then fit and the stored-tiles kernels run, head by head
+    free_bytes, _ = torch.cuda.mem_get_info(device)
+    roomy = free_bytes > (60 << 30)
+    if dist is not None:
+        flag = torch.tensor([int(roomy)], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        roomy = bool(flag.item())
+    if roomy:
+        old_budget = sb.set_backward_scratch_budget(40 << 30)
+        try:
+            if dist is not None:
+                dist.barrier()
+            _, ms = run_op(mine, w4["lengths"], steps)
+        finally:
+            sb.set_backward_scratch_budget(old_budget)
+        result["long_context_by_heads_scratch_40GiB"] = summarise(
+            w4, rank_times(ms), {"heads_per_rank": h1 - h0, "backward": "stored-tiles kernels, one head per chunk"})
     del full, mine, outs
     torch.cuda.empty_cache()
 

@@ -37,8 +37,9 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 // exact zero (V under P = 0, K under dz = 0, Q and dO under zero rows of dz and A) they are cleared first: 0 x NaN and
 // 0 x Inf are NaN.  Called by `nthreads` threads with indices `tid`; the caller fences (generic -> async proxy)
 // before it signals the MMA issuer.
-__device__ __forceinline__ void zero_tile_rows(uint8_t *tile, int row0, int box_rows, int boxes, int box_bytes, int tid,
-                                               int nthreads) {
+// (Not inlined: it runs once per sequence end, and the row loops it is called from are register-bound.)
+static __device__ __noinline__ void zero_tile_rows(uint8_t *tile, int row0, int box_rows, int boxes, int box_bytes, int tid,
+                                            int nthreads) {
   const int chunks = (box_rows - row0) * 8;   // 16-byte chunks per box
   for (int i = tid; i < chunks * boxes; i += nthreads) {
     const int b = i / chunks, c = i - b * chunks;

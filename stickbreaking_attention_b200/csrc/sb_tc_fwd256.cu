@@ -42,9 +42,13 @@ struct Cfg {
   // them: a stage is reloaded only after both tiles' P V MMAs of its step, so with three stages the load for step
   // s + 3 starts one row pass before its scores are wanted, which the ~2000 clk load latency does not always meet
   static constexpr int kStages = D == 64 ? 6 : 3;
-  static constexpr int kSmem = 1024 + 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
+  // Q tiles of two items at 64 columns (there is room): the next item's Q is loaded while the current item still
+  // reads its own, so a short item does not wait a load latency for its first scores
+  static constexpr int kQBufs = D == 64 ? 2 : 1;
+  static constexpr int kSmem = 1024 + kQBufs * 2 * kQBytes + kStages * kStageBytes + 4 * kPBytes + kBarBytes;
 };
-enum { bQ = 0, bKvFull = 1, bKvEmpty = 7, bSFull = 13, bQFree = 17, bOFree = 18, bPFull = 20, bPEmpty = 24, bOFull = 28, bNum = 30 };
+enum { bQ = 0, bKvFull = 1, bKvEmpty = 7, bSFull = 13, bQFree = 17, bOFree = 18, bPFull = 20, bPEmpty = 24, bOFull = 28, bQ2 = 30,
+       bQFree2 = 31, bNum = 32 };   // bQ2 / bQFree2: the second Q buffer
 static_assert(bKvEmpty - bKvFull == kMaxStages && bSFull - bKvEmpty == kMaxStages, "barrier slots per stage");
 // per-warpgroup barrier index: base + wg * 2 + buf
 }  // namespace fwd256
@@ -159,7 +163,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   using namespace fwd256;
   using C = Cfg<D>;
   constexpr int kQBytes = C::kQBytes, kKvTileBytes = C::kKvTileBytes, kStageBytes = C::kStageBytes, kBoxes = C::kBoxes;
-  constexpr int kStages = C::kStages;
+  constexpr int kStages = C::kStages, kQBufs = C::kQBufs;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) trace_block(p, 0);
   if (p.hdr[0]) return;
@@ -167,8 +171,8 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *gbase = smem_raw + (base - raw);
-  const uint32_t sQ = base;                             // Q_a, Q_b
-  const uint32_t sKV = sQ + 2 * kQBytes;                // stages: K sub-tile then V sub-tile
+  const uint32_t sQ = base;                             // per buffer: Q_a, Q_b
+  const uint32_t sKV = sQ + kQBufs * 2 * kQBytes;       // stages: K sub-tile then V sub-tile
   const uint32_t sP = sKV + kStages * kStageBytes;      // P[wg][buf]
   const uint32_t sBar = sP + 4 * kPBytes;
   uint8_t *gP = gbase + (sP - base);
@@ -182,6 +186,8 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(bar(bQ), 1);
     mbar_init(bar(bQFree), 2);
+    mbar_init(bar(bQ2), 1);
+    mbar_init(bar(bQFree2), 2);
     for (int s = 0; s < kStages; ++s) { mbar_init(bar(bKvFull + s), 1); mbar_init(bar(bKvEmpty + s), 2); }
     for (int s = 0; s < 4; ++s) {
       mbar_init(bar(bSFull + s), 1);
@@ -211,13 +217,15 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
       int T = 0;   // K/V stages filled so far
       for (int it = 0; fwd256_item(p, it, w); ++it) {
-        // Q of the previous item is no longer read once both issuers have finished its last S MMAs
-        if (it >= 1 && !wait_or_abort(bar(bQFree), (it - 1) & 1, abort_flag, p, 311)) break;
+        // the Q buffer's previous item (kQBufs items back) is no longer read once both issuers have finished its last S MMAs
+        const int qb = it % kQBufs, qn = it / kQBufs;     // buffer and how many items it has held before
+        const uint32_t bar_q = bar(qb ? bQ2 : bQ), bar_qfree = bar(qb ? bQFree2 : bQFree);
+        if (qn >= 1 && !wait_or_abort(bar_qfree, (qn - 1) & 1, abort_flag, p, 311)) break;
         const int qrow = (int)w.c.tok0 + w.blk_row0;
-        mbar_arrive_expect_tx(bar(bQ), 2 * kQBytes);
+        mbar_arrive_expect_tx(bar_q, 2 * kQBytes);
         for (int t = 0; t < 2; ++t)
           for (int kb = 0; kb < kBoxes; ++kb)
-            tma_load_4d(sQ + t * kQBytes + kb * kBoxBytes, &tm_q, bar(bQ), kb * 64, qrow + t * kBM, w.h, (int)w.c.boff);
+            tma_load_4d(sQ + (qb * 2 + t) * kQBytes + kb * kBoxBytes, &tm_q, bar_q, kb * 64, qrow + t * kBM, w.h, (int)w.c.boff);
         bool ok = true;
         for (int t = 0; t < w.n_steps; ++t) {
           const int g = T + t, st = g % kStages;
@@ -242,7 +250,6 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, kFp16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(kBM, D, kFp16, false, true);
-      const uint32_t qaddr = sQ + wg * kQBytes;
       int T = 0, U = 0;   // K/V stages and this tile's steps of the earlier items
       bool ok = true;
       for (int it = 0; ok && fwd256_item(p, it, w); ++it) {
@@ -255,7 +262,10 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = wait_or_abort(bar(bKvFull + g % kStages), (g / kStages) & 1, abort_flag, p, 324);
           if (ok) mbar_arrive(bar(bKvEmpty + g % kStages));
         }
-        if (ok && active) ok = wait_or_abort(bar(bQ), it & 1, abort_flag, p, 320);
+        const int qb = it % kQBufs, qn = it / kQBufs;
+        const uint32_t qaddr = sQ + (qb * 2 + wg) * kQBytes, bar_qfree = bar(qb ? bQFree2 : bQFree);
+        // (an idle issuer waits too: a parity wait is only meaningful for a waiter that follows every phase)
+        if (ok) ok = wait_or_abort(bar(qb ? bQ2 : bQ), qn & 1, abort_flag, p, 320);
         // Iteration u issues S(u) and then P V of step u-1, so that the next scores are being computed while the
         // rows of the current step are processed.  S(u) reuses the TMEM slot of step u-2, whose rows were finished
         // before p_full(u-2) was signalled, and that was waited for in iteration u-1.
@@ -269,7 +279,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             mma_kmajor_kmajor<D, kBoxBytes, kKvBoxBytes>(tmem + wg * 128 + (gu & 1) * 64, qaddr, sKV + st * kStageBytes, idesc_s,
                                                          false);
             mma_commit(bar(bSFull + wg * 2 + (gu & 1)));
-            if (u == my_steps - 1) mma_commit(bar(bQFree));   // the item's last read of Q
+            if (u == my_steps - 1) mma_commit(bar_qfree);   // the item's last read of Q
             trace_event(p, 1 + 3 * wg, tr_cur, 3 + 16 * wg, t0 + u);
           }
           if (u >= 1) {
@@ -294,7 +304,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
         if (!ok) break;
-        if (!active) mma_commit(bar(bQFree));   // after this thread's earlier MMAs, like every arrival on these two
+        if (!active) mma_commit(bar_qfree);   // after this thread's earlier MMAs, like every arrival on these two
         mma_commit(bar(bOFull + wg));   // this tile's O is complete (an idle tile: behind its earlier MMAs)
         T += w.n_steps;
         U += my_steps;

@@ -157,7 +157,16 @@ def _run(backward: bool, prm, device):
     need = lib.sb_workspace_bytes(prm, int(backward))
     if need == 2 ** 64 - 1:
         raise _cabi.SbError(f"invalid parameters: {lib.sb_last_error().decode()}")
-    workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+    try:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+    except torch.cuda.OutOfMemoryError:
+        # the stored-tiles backward asks for up to the scratch budget; where the reference would still fit (its backward
+        # keeps O(tokens) state), fall back to the recomputing kernels and their few MB instead of failing
+        if not backward or prm.flags & _cabi.SB_FLAG_BWD_RECOMPUTE:
+            raise
+        prm.flags |= _cabi.SB_FLAG_BWD_RECOMPUTE
+        need = lib.sb_workspace_bytes(prm, 1)
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
     prm.workspace = workspace.data_ptr()
     prm.workspace_bytes = workspace.numel()
     prm.status = _status_word(device).data_ptr()
