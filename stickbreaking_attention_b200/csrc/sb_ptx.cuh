@@ -5,6 +5,10 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#ifndef SB_MBAR_HINT_NS
+#define SB_MBAR_HINT_NS 100000u
+#endif
+
 namespace sb {
 namespace ptx {
 
@@ -27,14 +31,16 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One try: returns at once if the phase has completed; otherwise the hardware may park the thread until the phase
+// completes or the hint (nanoseconds) has passed, so a waiting warp does not spend its scheduler's issue slots polling.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(SB_MBAR_HINT_NS)
       : "memory");
   return ok != 0;
 }
@@ -47,13 +53,11 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int spin = 0; spin < 4096; ++spin)
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (int spin = 0; spin < (1 << 24); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() - t0 > 1000000000ull) return false;
-    __nanosleep(64);
   }
   return false;
 }
