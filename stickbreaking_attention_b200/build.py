@@ -18,8 +18,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libsb_b200.so")
-SOURCES = ("sb_api.cu", "sb_simt.cu", "sb_tc.cu", "sb_tc_fwd256.cu", "sb_tc_bwd.cu")
-HEADERS = ("sb_common.cuh", "sb_ptx.cuh", "sb_tc_common.cuh", "../../include/sb_b200.h")
+SOURCES = ("sb_api.cu", "sb_simt.cu", "sb_tc.cu", "sb_tc_fwd256.cu", "sb_tc_fwd128.cu", "sb_tc_bwd.cu")
+HEADERS = ("sb_common.cuh", "sb_ptx.cuh", "sb_tc_common.cuh", "sb_tc_fwd_rows.cuh", "../../include/sb_b200.h")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xptxas", "-v",

@@ -87,10 +87,10 @@ static int make_plan(const SbParams *p, Plan &pl, bool backward) {
   for (const SbTensor *t : others)
     if (t->ptr != nullptr && !tma_friendly(*t, esize)) tc = false;
   pl.path = tc ? SB_PATH_TCGEN05 : SB_PATH_SIMT;
-  pl.tile = tc ? tc_tile(p->head_dim, backward) : kSimtTile;
   const long long T = p->tokens;
   pl.max_seqlen = (p->max_seqlen == 0 || p->max_seqlen > T) ? (int)T : p->max_seqlen;
   if (p->cu_seqlens == nullptr) pl.max_seqlen = (int)T;
+  pl.tile = tc ? tc_tile(p->head_dim, backward, pl.max_seqlen) : kSimtTile;
   const long long n_all = (T + pl.tile - 1) / pl.tile;
   pl.n_max = (int)((pl.max_seqlen + pl.tile - 1) / pl.tile);
   if (p->cu_seqlens == nullptr) {

@@ -158,8 +158,9 @@ cudaError_t launch_simt_bwd(const KParams &p, int dtype, cudaStream_t s, int *la
 cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
 cudaError_t launch_tc_bwd(const KParams &p, int dtype, cudaStream_t s, int *launches);
 bool tc_supported(int dtype, int head_dim, bool backward);
-int tc_tile(int head_dim, bool backward);   // rows per work item of the tensor-core kernels
+int tc_tile(int head_dim, bool backward, int max_seqlen);   // rows per work item of the tensor-core kernels
 cudaError_t launch_tc_fwd256(const KParams &p, int dtype, cudaStream_t s);
+cudaError_t launch_tc_fwd128(const KParams &p, int dtype, cudaStream_t s);
 cudaError_t sm_count(int *out);              // SMs of the current device (cached)
 
 constexpr size_t kTraceBytes = 8 * 1024 * 16;   // workspace tail reserved for the event log

@@ -1,6 +1,10 @@
 // Host side of the tensor-core path: TMA tensor maps, which shapes take the path, the forward dispatch.
 #include <cstring>
 
+#ifndef SB_SHORT_SEQ
+#define SB_SHORT_SEQ 1024
+#endif
+
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -102,10 +106,13 @@ cudaError_t make_az_map(CUtensorMap *map, const KParams &p, int dtype, int box_r
   return encode_cached(map, p.az, dims, strides, box_rows, dtype);
 }
 
-// The forward for head sizes above 64 works on 256 query rows per CTA (two 128-row tiles sharing the K/V stream).
-int tc_tile(int head_dim, bool backward) {
-  (void)head_dim;
-  return backward ? kBM : 256;
+// The forward works on 256 query rows per item (two 128-row tiles sharing the K/V stream), except for head sizes up
+// to 64 with sequences of at most kShortSeq tokens (the caller's max_seqlen bound), where two independent 128-row
+// tiles per block do better (sb_tc_fwd128.cu).
+constexpr int kShortSeq = SB_SHORT_SEQ;
+int tc_tile(int head_dim, bool backward, int max_seqlen) {
+  if (backward) return kBM;
+  return (head_dim <= 64 && max_seqlen <= kShortSeq) ? kBM : 256;
 }
 
 cudaError_t sm_count(int *out) {
@@ -130,7 +137,7 @@ bool tc_supported(int dtype, int head_dim, bool backward) {
 
 cudaError_t launch_tc_fwd(const KParams &p, int dtype, cudaStream_t s, int *launches) {
   *launches += 1;
-  return launch_tc_fwd256(p, dtype, s);
+  return p.tile == kBM ? launch_tc_fwd128(p, dtype, s) : launch_tc_fwd256(p, dtype, s);
 }
 
 }  // namespace sb
