@@ -678,35 +678,54 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       float gs = 0.f, logsum = 0.f;
       const bool diag = (u == 0);
       const bool masked = diag || (I == c.n_tiles - 1 && (c.len & (kBM - 1)) != 0);
-      uint32_t s0[16], d0[16], s1[16], d1[16];
-      tmem_ld16(tS, s0);
-      tmem_ld16(tP, d0);
-      tmem_wait_ld_regs(s0, d0);
-      tmem_ld16(tS + 16, s1);
-      tmem_ld16(tP + 16, d1);
-      {
-        float pa[16], pz[16];
+      // On the diagonal tile the quarters after this warp's last row are masked for all of its 32 rows, and a warp whose
+      // rows all lie past the sequence end has nothing allowed anywhere: A and dz are zero, the scores are not read.
+      const bool skip = (diag && quarter * 32 >= (r | 31) + p.attend_current) || I * kBM + (r & ~31) >= c.len;
+      if (!skip) {
+        uint32_t s0[16], d0[16], s1[16], d1[16];
+        tmem_ld16(tS, s0);
+        tmem_ld16(tP, d0);
+        tmem_wait_ld_regs(s0, d0);
+        tmem_ld16(tS + 16, s1);
+        tmem_ld16(tP + 16, d1);
+        {
+          float pa[16], pz[16];
+          if (masked)
+            bwd_row_chunk_values<true>(s0, d0, quarter * 32, r, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
+          else
+            bwd_row_chunk_values<false>(s0, d0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
+          // the A/dz tiles are still being read by the previous step's MMAs
+          if (g >= 1) {
+            ok = wait_or_abort(bar(bAzEmpty), (g - 1) & 1, abort_flag, p, 631);
+            tc_fence_after();
+          }
+          store_row_chunk16<kFp16>(gA, r, w * 32, pa);
+          store_row_chunk16<kFp16>(gZ, r, w * 32, pz);
+        }
+        tmem_wait_ld_regs(s1, d1);
+        tc_fence_before();          // this step's TMEM reads are done: the S/dP slot is handed back
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(bSpEmpty + slot));
         if (masked)
-          bwd_row_chunk_values<true>(s0, d0, quarter * 32, r, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
+          bwd_row_chunk<kFp16, true, true>(s1, d1, w * 32 + 16, quarter * 32 + 16, r, diag, p.attend_current, valid, scale2, r1f,
+                                           gpre, dr, gs, logsum, gA, gZ);
         else
-          bwd_row_chunk_values<false>(s0, d0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
-        // the A/dz tiles are still being read by the previous step's MMAs
+          bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+      } else {
         if (g >= 1) {
           ok = wait_or_abort(bar(bAzEmpty), (g - 1) & 1, abort_flag, p, 631);
           tc_fence_after();
         }
-        store_row_chunk16<kFp16>(gA, r, w * 32, pa);
-        store_row_chunk16<kFp16>(gZ, r, w * 32, pz);
+        const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          store_packed_chunk16(gA, r, w * 32 + 16 * q, zero);
+          store_packed_chunk16(gZ, r, w * 32 + 16 * q, zero);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(bSpEmpty + slot));
       }
-      tmem_wait_ld_regs(s1, d1);
-      tc_fence_before();          // this step's TMEM reads are done: the S/dP slot is handed back
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(bSpEmpty + slot));
-      if (masked)
-        bwd_row_chunk<kFp16, true, true>(s1, d1, w * 32 + 16, quarter * 32 + 16, r, diag, p.attend_current, valid, scale2, r1f,
-                                         gpre, dr, gs, logsum, gA, gZ);
-      else
-        bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
       // the sequence ends inside this query tile: the A and dz rows behind the end are exact zeros, the Q and dO rows
       // there are not this sequence's (see zero_tile_rows) and are cleared before this step's MMAs are released
       if (c.len - I * kBM < kBM)

@@ -23,7 +23,7 @@ constexpr int kBN = 64;                       // keys per sub-tile
 constexpr int kQBytes = kBM * D * 2;          // one 128-row Q tile = one 128 x 64 box
 constexpr int kKvTileBytes = kBN * D * 2;     // K or V sub-tile: one 64 x 64 box
 constexpr int kStageBytes = 2 * kKvTileBytes;
-constexpr int kStages = 3;
+constexpr int kStages = 3;                    // (a fourth stage fits and was measured: no gain)
 constexpr int kQBufs = 2;
 constexpr int kOBytes = kBM * D * 2;          // staging tile of the O epilogue
 constexpr int kWorkerBytes = kQBufs * kQBytes + kStages * kStageBytes + kOBytes;
@@ -31,7 +31,8 @@ constexpr int kBarBytes = 512;
 constexpr int kSmem = 1024 + 2 * kWorkerBytes + kBarBytes;
 constexpr uint32_t kWorkerCols = 192;
 // barriers of one worker
-enum { bQ = 0, bQFree = 2, bKvFull = 4, bKvEmpty = 7, bSFull = 10, bPFull = 12, bOFull = 14, bOFree = 15, bPerWorker = 16 };
+enum { bQ = 0, bQFree = 2, bKvFull = 4, bKvEmpty = 4 + kStages, bSFull = 4 + 2 * kStages, bPFull = bSFull + 2, bOFull = bSFull + 4,
+       bOFree = bSFull + 5, bPerWorker = bSFull + 6 };
 }  // namespace fwd128
 
 struct Fwd128Item {
@@ -190,6 +191,7 @@ tc_fwd128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int it = 0; ok && have; ++it) {
       const int row = w.row0 + r;                    // row index inside the sequence
       const int s_diag0 = 2 * w.c.idx;               // first sub-tile that reaches this tile's diagonal band
+      const bool warp_live = (row & ~31) < w.c.len;  // a warp whose 32 rows all lie past the sequence end computes nothing
       double run = 0.0;
       if (lane == 0) tma_store_wait_read();          // the previous tile's O has left the staging tile
       __syncwarp();
@@ -209,7 +211,9 @@ tc_fwd128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         float R = ex2(-(float)run);
         float logsum = 0.f;
-        if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, nullptr, r, ts + kPCol);
+        // (the P rows of such a warp keep whatever the slot held: they only reach accumulator rows that are never stored)
+        if (!warp_live) {
+        } else if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, nullptr, r, ts + kPCol);
         else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, nullptr, r, ts + kPCol);
         run += (double)logsum;
         tmem_wait_st();

@@ -247,6 +247,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int my_steps = active ? w.n_steps - t0 : 0;
       const int row = w.blk_row0 + wg * kBM + r;       // row index inside the sequence
       const int s_diag0 = 4 * w.c.idx + 2 * wg;        // first sub-tile that reaches this tile's diagonal band
+      const bool warp_live = (row & ~31) < w.c.len;    // a warp whose 32 rows all lie past the sequence end computes nothing
       double run = 0.0;
       if (lane == 0) tma_store_wait_read();   // the previous item's O has left the P buffers
       __syncwarp();
@@ -275,7 +276,9 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         float R = ex2(-(float)run);
         float logsum = 0.f;
         // 64 columns in chunks of 16, last chunk first; TMEM is read one chunk ahead of the arithmetic
-        if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
+        // (the P rows of such a warp keep whatever their buffer held: they only reach accumulator rows that are never stored)
+        if (!warp_live) {
+        } else if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
         else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
         run += (double)logsum;
         if constexpr (kPTmem) tmem_wait_st();

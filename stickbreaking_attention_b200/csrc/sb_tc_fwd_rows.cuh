@@ -76,13 +76,40 @@ __device__ __forceinline__ void fwd256_row_chunk(const uint32_t (&v)[16], int c0
   }
 }
 
+// P of 32 key columns (from column c0 of the sub-tile on) set to zero without looking at the scores.
+template <bool kFp16>
+__device__ __forceinline__ void fwd256_zero_pair(int c0, uint8_t *tile_p, int r, uint32_t tmem_p) {
+  if constexpr (kPTmem) {
+    const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    tmem_st8(tmem_p + (c0 >> 1), z);
+    tmem_st8(tmem_p + (c0 >> 1) + 8, z);
+  } else {
+    const float z[16] = {};
+    store_row_chunk16<kFp16>(tile_p, r, c0, z);
+    store_row_chunk16<kFp16>(tile_p, r, c0 + 16, z);
+  }
+}
+
+// One row of a 64-key sub-tile.  In a masked sub-tile the columns from (last row of this warp) + ac on are masked for
+// every row of the warp (its 32 rows are consecutive and 32-aligned): such 32-column halves are not computed at all,
+// their P is zero and R and logsum stay as they are -- 6 of the 16 (warp, half) pairs of a diagonal 128 x 128 tile.
 template <bool kFp16, bool kMasked>
 __device__ __forceinline__ void fwd256_row_pass(uint32_t ts, int key0, int row, int ac, float scale2, float &R,
                                                 float &logsum, uint8_t *tile_p, int r, uint32_t tmem_p) {
+  int hi = 1;   // last 32-column half with an allowed key
+  if (kMasked) {
+    const int span = (row | 31) + ac - key0;   // the warp's rows may attend to columns [0, span) of this sub-tile
+    hi = span > 32 ? 1 : (span > 0 ? 0 : -1);
+    if (hi < 1) fwd256_zero_pair<kFp16>(32, tile_p, r, tmem_p);
+    if (hi < 0) {
+      fwd256_zero_pair<kFp16>(0, tile_p, r, tmem_p);
+      return;
+    }
+  }
   uint32_t va[16], vb[16];
-  tmem_ld16(ts + 48, va);
+  tmem_ld16(ts + hi * 32 + 16, va);
 #pragma unroll 1
-  for (int pair = 1; pair >= 0; --pair) {
+  for (int pair = hi; pair >= 0; --pair) {
     tmem_wait_ld_regs(va);
     tmem_ld16(ts + pair * 32, vb);
     fwd256_row_chunk<kFp16, kMasked>(va, pair * 32 + 16, key0 + pair * 32 + 16, row, ac, scale2, R, logsum, tile_p, r, tmem_p);
