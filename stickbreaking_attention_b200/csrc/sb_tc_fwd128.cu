@@ -12,6 +12,11 @@
 //   warps 9 / 10      MMA issuers of worker 0 / 1: S = Q K^T (128x64x64) into a double-buffered TMEM slot,
 //                     O += P V (128x64x64) with P read from tensor memory
 // TMEM columns of worker w: S[2] at 192 w + {0, 64}, O at 192 w + 128.  All waits are bounded.
+//
+// Row warp j of either worker runs on scheduler j of the SM, and the later rows of a tile have more allowed keys in the
+// diagonal band (and are the ones missing when the sequence ends inside the tile).  Worker 1 therefore holds its tile
+// with the four 32-row blocks in reverse order (Q is loaded as four 32-row boxes, tensor-memory lanes 0..31 are query
+// rows 96..127 of the tile): every scheduler then serves one warp with much and one with little work.
 #include "sb_tc_fwd_rows.cuh"
 
 namespace sb {
@@ -118,7 +123,9 @@ tc_fwd128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // the buffer's previous tile is no longer read once its last S MMA has finished
         if (qn >= 1 && !wait_or_abort(bar(bQFree + qb), (qn - 1) & 1, abort_flag, p, 711)) break;
         mbar_arrive_expect_tx(bar(bQ + qb), kQBytes);
-        tma_load_4d(sQ + qb * kQBytes, &tm_q, bar(bQ + qb), 0, (int)w.c.tok0 + w.row0, w.h, (int)w.c.boff);
+        for (int b = 0; b < 4; ++b)   // block b of the shared-memory tile (= TMEM lanes 32 b ..) holds row block wk ? 3 - b : b
+          tma_load_4d(sQ + qb * kQBytes + b * (kQBytes / 4), &tm_q, bar(bQ + qb), 0,
+                      (int)w.c.tok0 + w.row0 + (wk ? 3 - b : b) * 32, w.h, (int)w.c.boff);
         bool ok = true;
         for (int t = 0; t < w.n_steps; ++t) {
           const int g = T + t, st = g % kStages;
@@ -179,7 +186,8 @@ tc_fwd128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   } else {
     // ------------------------------------------------ one thread per query row
     using T = typename std::conditional<kFp16, __half, __nv_bfloat16>::type;
-    const int r = threadIdx.x & 127;                 // row inside the tile == TMEM lane
+    const int r = threadIdx.x & 127;                 // TMEM lane == row of the shared-memory tiles
+    const int blk = wk ? 3 - (warp & 3) : (warp & 3); // which 32-row block of the query tile this warp's lanes hold
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float scale2 = p.scale * kLog2e;
     const int ac = p.attend_current;
@@ -189,7 +197,7 @@ tc_fwd128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     bool have = fwd128_item(p, 0, v, V, w);
     uint8_t *stage = gbase + (sO - base);
     for (int it = 0; ok && have; ++it) {
-      const int row = w.row0 + r;                    // row index inside the sequence
+      const int row = w.row0 + blk * 32 + lane;      // row index inside the sequence
       const int s_diag0 = 2 * w.c.idx;               // first sub-tile that reaches this tile's diagonal band
       const bool warp_live = (row & ~31) < w.c.len;  // a warp whose 32 rows all lie past the sequence end computes nothing
       double run = 0.0;
@@ -244,7 +252,7 @@ tc_fwd128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_4d(&tm_o, sO + (warp & 3) * 32 * 128, 0, (int)w.c.tok0 + w.row0 + (warp & 3) * 32, w.h, (int)w.c.boff);
+            tma_store_4d(&tm_o, sO + (warp & 3) * 32 * 128, 0, (int)w.c.tok0 + w.row0 + blk * 32, w.h, (int)w.c.boff);
             tma_store_commit();
           }
         } else {
@@ -273,8 +281,8 @@ template <bool kFp16>
 static cudaError_t launch128_t(const KParams &p, int dtype, cudaStream_t s) {
   CUtensorMap mq, mk, mv, mo;
   cudaError_t e;
-  if ((e = make_tile_map(&mq, p.q, p, dtype, kBM)) != cudaSuccess) return e;
-  if ((e = make_tile_map(&mo, p.o, p, dtype, 32)) != cudaSuccess) return e;   // stores: 32 rows per warp
+  if ((e = make_tile_map(&mq, p.q, p, dtype, 32)) != cudaSuccess) return e;   // loads and stores: 32-row blocks
+  if ((e = make_tile_map(&mo, p.o, p, dtype, 32)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mk, p.k, p, dtype, fwd128::kBN)) != cudaSuccess) return e;
   if ((e = make_tile_map(&mv, p.v, p, dtype, fwd128::kBN)) != cudaSuccess) return e;
   int sms = 0;
