@@ -426,6 +426,23 @@ def test_tensor_core_and_cuda_core_paths_agree(sb, cuda_device, d):
         assert H.rel_l2(a, b) <= 5e-2, name
 
 
+@pytest.mark.parametrize("ac", [False, True])
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 64), (torch.float16, 32), (torch.bfloat16, 40)])
+def test_both_forward_kernels_for_small_heads(sb, cuda_device, dtype, d, ac):
+    """Head sizes up to 64 run the two-tiles-per-block forward kernel while max_seqlens <= 1024 and the 256-row kernel
+    above: the same batch through both (the bound is the caller's, so a larger one is legal) against the oracle, and
+    against each other -- both do the same arithmetic in the same order, so the outputs are equal bit for bit."""
+    lengths = [1, 33, 96, 97, 128, 129, 255, 256, 257, 383, 500, 1000, 1024, 31, 640]
+    ins = H.make_inputs((3, sum(lengths), d), dtype, seed=41 + d, std=1.0)
+    cu = cu_of(lengths)
+    short = H.run_varlen(sb, *ins, cu, cuda_device, attend_current=ac, max_seqlens=max(lengths))
+    long_ = H.run_varlen(sb, *ins, cu, cuda_device, attend_current=ac, max_seqlens=4096)
+    want = H.oracle_varlen(*ins, cu, attend_current=ac)
+    H.assert_parity(short, want, dtype, "two tiles per block")
+    H.assert_parity(long_, want, dtype, "256-row items")
+    assert torch.equal(short[0], long_[0]) and torch.equal(short[1], long_[1])
+
+
 # ---- error behaviour: failures are made on the host, never by faulting the device -----------------------
 
 def test_bad_cu_seqlens_is_reported_not_executed(sb, cuda_device):
