@@ -805,26 +805,31 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // dK/dV from stored tiles (head sizes 72..128): two GEMMs per 128-key tile, no row passes
 // =======================================================================================================
 // In stored-tiles mode the dq kernel leaves the 16-bit A and dz tiles of every (query tile, key tile) pair in the
-// workspace.  This kernel owns one 128-key tile and walks its query tiles diagonal -> end, 64 query rows per stage:
-//   dK[keys x d] += dz^T Q,   dV[keys x d] += A^T dO      (M = 128 keys, N = 128 columns, K = 64 query rows)
+// workspace.  This kernel owns one 128-key tile and walks its query tiles diagonal -> end, 32 query rows per stage:
+//   dK[keys x d] += dz^T Q,   dV[keys x d] += A^T dO      (M = 128 keys, N = 128 columns, K = 32 query rows)
 // with all four operands read row-major as "MN-major" tiles (rows = query rows = the contraction).  Accumulators sit
 // in TMEM with lanes = keys, so the epilogue writes plain rows.  Fixed summation order, no atomics.
-//   warp 4    TMA producer: per stage A, dz (from the workspace), Q, dO -- 64 KiB, three stages
+//   warp 4    TMA producer: per stage A, dz (from the workspace), Q, dO -- 32 KiB, three stages
 //   warp 5    MMA issuer
 //   warps 0-3 epilogue: dK, dV rows -> shared memory -> TMA stores
-// The kernel is bound by reading the stored tiles (64 KiB per 128x128 pair) from HBM.
+// The kernel is bound by reading the stored tiles (64 KiB per 128x128 pair) from HBM.  A block has a fixed cost of
+// several microseconds (first loads, and at the end accumulators -> shared memory -> TMA stores) next to ~17 stages
+// on average, so the stages are kept small enough for TWO blocks per SM (100 KB of shared memory, 256 TMEM columns
+// each): one block's prologue and epilogue run under the other's stages.
 namespace dkv5 {
 constexpr int kThreads = 192;
 constexpr int kStages = 3;
-constexpr int kBox = 64 * 64 * 2;            // 64 rows x 64 columns, 16-bit
-constexpr int kStageBytes = 8 * kBox;        // A, dz, Q, dO: two 64-column blocks each
+constexpr int kRows = 32;                    // query rows per stage
+constexpr int kSub = kBM / kRows;            // stages per query tile
+constexpr int kBox = kRows * 64 * 2;         // kRows rows x 64 columns, 16-bit
+constexpr int kStageBytes = 8 * kBox;        // A, dz, Q, dO: two 64-column blocks each; also one 128 x 128 output tile
 constexpr int kSmem = 1024 + kStages * kStageBytes + 512;
 constexpr uint32_t kCols = 256;              // dK 0..127, dV 128..255
 enum { bFull = 0, bEmpty = 3, bOut = 6, bClean = 7, bLanded = 8, bNum = 9 };
 }  // namespace dkv5
 
 template <bool kFp16>
-__global__ void __launch_bounds__(dkv5::kThreads, 1)
+__global__ void __launch_bounds__(dkv5::kThreads, 2)
 tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_dk,
                    const __grid_constant__ CUtensorMap tm_dv, const KParams p) {
@@ -837,14 +842,14 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
   if (!decode_block(p, 1, false, c, hh)) return;
   const int h = p.head0 + hh;
   const int J = c.idx;                        // the 128-key tile
-  const int n_stages = 2 * (c.n_tiles - J);   // stage t: query tile J + (t >> 1), rows (t & 1) * 64 .. + 64
+  const int n_stages = kSub * (c.n_tiles - J);   // stage t: query tile J + t / kSub, rows (t % kSub) * kRows .. + kRows
   // The sequence may end inside the last query tile.  The A and dz rows behind the end are zeros in the workspace; the
   // Q and dO rows there are not this sequence's (see zero_tile_rows).  Stages from t_clean on hold such rows: the
   // issuer tells the epilogue warps, idle until the end, that such a stage has landed (bLanded; a barrier of its own,
   // because a parity wait on bFull only works for a waiter that follows every phase), they clear the rows and hand
   // the stage back through bClean.
   const int last_rows = c.len - (c.n_tiles - 1) * kBM;          // 1 .. 128 rows of the last query tile exist
-  const int t_clean = last_rows >= kBM ? n_stages : (last_rows > 64 ? n_stages - 1 : n_stages - 2);
+  const int t_clean = last_rows >= kBM ? n_stages : n_stages - (kSub - last_rows / kRows);
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -879,10 +884,10 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
         const int st = t % kStages;
         if (t >= kStages && !wait_or_abort(bar(bEmpty + st), ((t / kStages) - 1) & 1, abort_flag, p, 640)) break;
         if (*abort_flag) break;
-        const int I = J + (t >> 1), hq = t & 1;
+        const int I = J + t / kSub, hq = t % kSub;
         const long long pair = c.pair0 + (long long)I * (I + 1) / 2 + J;
-        const int az_row = (int)(pair * kBM) + hq * 64;
-        const int qrow = (int)c.tok0 + I * kBM + hq * 64;
+        const int az_row = (int)(pair * kBM) + hq * kRows;
+        const int qrow = (int)c.tok0 + I * kBM + hq * kRows;
         const uint32_t dst = base + st * kStageBytes;
         mbar_arrive_expect_tx(bar(bFull + st), kStageBytes);
         for (int kb = 0; kb < 2; ++kb) {
@@ -911,10 +916,10 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
         const uint64_t dA = smem_desc_sw128(a, kBox, 1024), dZ = smem_desc_sw128(a + 2 * kBox, kBox, 1024);
         const uint64_t dQ = smem_desc_sw128(a + 4 * kBox, kBox, 1024), dG = smem_desc_sw128(a + 6 * kBox, kBox, 1024);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)   // 16 query rows = 2048 bytes per step
+        for (int ks = 0; ks < kRows / 16; ++ks)   // 16 query rows = 2048 bytes per step
           mma_f16_ss(tmem, dZ + (uint64_t)(ks * 128), dQ + (uint64_t)(ks * 128), idesc, t > 0 || ks > 0);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
+        for (int ks = 0; ks < kRows / 16; ++ks)
           mma_f16_ss(tmem + 128, dA + (uint64_t)(ks * 128), dG + (uint64_t)(ks * 128), idesc, t > 0 || ks > 0);
         mma_commit(bar(bEmpty + st));
       }
@@ -930,9 +935,9 @@ tc_bwd_dkv5_kernel(const __grid_constant__ CUtensorMap tm_az, const __grid_const
       const int st = t % kStages;
       ok = wait_or_abort(bar(bLanded), (t - t_clean) & 1, abort_flag, p, 644);
       if (!ok) break;
-      int keep = last_rows - (t & 1) * 64;   // rows of this stage that belong to the sequence
+      int keep = last_rows - (t % kSub) * kRows;   // rows of this stage that belong to the sequence
       keep = keep < 0 ? 0 : keep;
-      zero_tile_rows(gbase + st * kStageBytes + 4 * kBox, keep, 64, 4, kBox, r, kBM);   // Q and dO: boxes 4..7 of the stage
+      zero_tile_rows(gbase + st * kStageBytes + 4 * kBox, keep, kRows, 4, kBox, r, kBM);   // Q and dO: boxes 4..7 of the stage
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(bClean));
@@ -1011,9 +1016,9 @@ static cudaError_t launch_bwd_t(const KParams &p, int dtype, cudaStream_t s) {
     e = allow_dynamic_smem(reinterpret_cast<const void *>(kernel), dkv5::kSmem);
     if (e != cudaSuccess) return e;
     CUtensorMap maz, mq64, mg64, mdk, mdv;
-    if ((e = make_az_map(&maz, p, dtype)) != cudaSuccess) return e;
-    if ((e = make_tile_map(&mq64, p.q, p, dtype, 64)) != cudaSuccess) return e;
-    if ((e = make_tile_map(&mg64, p.d_o, p, dtype, 64)) != cudaSuccess) return e;
+    if ((e = make_az_map(&maz, p, dtype, dkv5::kRows)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mq64, p.q, p, dtype, dkv5::kRows)) != cudaSuccess) return e;
+    if ((e = make_tile_map(&mg64, p.d_o, p, dtype, dkv5::kRows)) != cudaSuccess) return e;
     if ((e = make_tile_map(&mdk, p.dk, p, dtype, 32)) != cudaSuccess) return e;   // stores: 32 rows per warp
     if ((e = make_tile_map(&mdv, p.dv, p, dtype, 32)) != cudaSuccess) return e;
     kernel<<<grid, dkv5::kThreads, dkv5::kSmem, s>>>(maz, mq64, mg64, mdk, mdv, p);
