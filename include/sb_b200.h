@@ -161,8 +161,9 @@ SB_EXPORT int sb_bwd(const SbParams *p, void *stream);
  *
  * Same results as sb_fwd.  A call fits when sb_workspace_bytes(p, 0) <= SB_STATIC_SCRATCH_BYTES; that is the whole
  * rule.  (The scratch holds the sequence table: a few hundred bytes plus about 12 bytes per packed sequence and 8
- * bytes per work item, an item being 256 tokens on the tensor-core path and 32 tokens on the CUDA-core path that
- * fp32 tensors and irregular head sizes take; a fixed-length batch always fits.)  A call that does not fit returns
+ * bytes per work item, an item being 256 tokens on the tensor-core path (128 tokens for head sizes up to 64 with
+ * max_seqlen <= 1024) and 32 tokens on the CUDA-core path that fp32 tensors and irregular head sizes take; a
+ * fixed-length batch always fits.)  A call that does not fit returns
  * SB_ERR_WORKSPACE with a message and launches nothing.  The function calls no cudaMalloc, cudaFree or any other
  * allocating routine.
  *
