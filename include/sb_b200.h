@@ -75,12 +75,20 @@ enum SbFlags {
                             two plain GEMMs over them.  With this flag, or when one head alone exceeds the
                             budget, the dK/dV kernel recomputes the tiles from boundary values (a few KiB
                             per pair).  Same 16-bit tiles either way.                             */
-  SB_FLAG_FUSE_REM_V = 32   /* the caller wants out = o + rem[..., None] * v, what every caller of the
+  SB_FLAG_FUSE_REM_V = 32,  /* the caller wants out = o + rem[..., None] * v, what every caller of the
                             reference computes right after the operator (tests/test_varlen.py:101,
                             tests/test_attn.py:64).  sb_fwd writes `out` to `o` (rem and log_rem as usual).
                             sb_bwd takes d_out in `d_o`, adds <d_out, v> per row to d_rem (which may then be
                             NULL = zero) and rem * d_out to dv, and needs 4 more workspace bytes per
                             (batch, head, token).                                                  */
+  SB_FLAG_DENSE_ROW_PASS = 64 /* measuring aid.  The attention weight of a key is its beta times the product of
+                            (1 - beta) over the keys between it and the query; in fp32 that product underflows to
+                            exactly 0 once the keys in between carry about 126 bits of -log2(1 - beta).  From
+                            there on everything a row computes per score (p in the forward; A, G and dz in the
+                            backward) is exactly 0, and the tensor-core kernels skip that arithmetic wherever it
+                            is 0 for all 32 rows of a warp: they keep only the running log-space sum.  Every MMA
+                            is still issued and the results are bit-identical.  With this flag the arithmetic is
+                            done for every score regardless.                                      */
 };
 
 typedef struct SbTensor {

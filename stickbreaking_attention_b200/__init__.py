@@ -13,13 +13,13 @@ from . import _cabi
 _cabi.load()   # fail at import time, loudly, if the CUDA library has not been built
 
 from . import ops, sb_attn as _sb_attn_mod, sb_varlen as _sb_varlen_mod  # noqa: E402
-from .ops import (check_status, force_simt, kernel_launches, kernel_path, set_backward_scratch_budget,  # noqa: E402
+from .ops import (check_status, dense_row_pass, force_simt, kernel_launches, kernel_path, set_backward_scratch_budget,  # noqa: E402
                   small_backward_workspace)
 from .sb_attn import sb_attn, sb_attn_fused  # noqa: E402
 from .sb_varlen import sb_attn_varlen, sb_attn_varlen_fused  # noqa: E402
 
 __all__ = ["sb_attn", "sb_attn_varlen", "sb_attn_fused", "sb_attn_varlen_fused", "check_status", "force_simt",
-           "small_backward_workspace", "set_backward_scratch_budget", "kernel_launches", "kernel_path", "install_as_dropin",
+           "small_backward_workspace", "dense_row_pass", "set_backward_scratch_budget", "kernel_launches", "kernel_path", "install_as_dropin",
            "ops"]
 
 

@@ -19,6 +19,7 @@ SB_STATIC_SCRATCH_BYTES = 65536
 SB_FLAG_FORCE_SIMT, SB_FLAG_CHECK_LEADING_ZERO, SB_FLAG_BWD_SKIP_DKV, SB_FLAG_BWD_SKIP_DQ = 1, 2, 4, 8
 SB_FLAG_BWD_RECOMPUTE = 16
 SB_FLAG_FUSE_REM_V = 32
+SB_FLAG_DENSE_ROW_PASS = 64
 SB_DEV_MESSAGES = {
     1: "cu_seqlens is invalid (not non-decreasing, beyond the token count, longer than max_seqlens, "
        "or without its leading zero); offending sequence index: {0}",

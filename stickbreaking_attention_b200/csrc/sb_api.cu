@@ -203,6 +203,7 @@ static int fill_kparams(const SbParams *p, const Plan &pl, bool backward, KParam
 #endif
   k.skip_dq = (p->flags & SB_FLAG_BWD_SKIP_DQ) ? 1 : 0;
   k.skip_dkv = (p->flags & SB_FLAG_BWD_SKIP_DKV) ? 1 : 0;
+  k.dense = (p->flags & SB_FLAG_DENSE_ROW_PASS) ? 1 : 0;
   k.tile = pl.tile; k.tiles_cap = pl.tiles_cap; k.n_max = pl.n_max; k.max_seqlen = pl.max_seqlen;
   char *ws = reinterpret_cast<char *>(p->workspace);
   k.hdr = reinterpret_cast<int *>(ws);

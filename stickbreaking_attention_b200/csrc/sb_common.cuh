@@ -38,6 +38,7 @@ struct KParams {
   int max_seqlen;
   int check_leading_zero;  // the element before cu[0] must be 0
   int skip_dq, skip_dkv;   // timing aids: leave one of the two backward kernels out
+  int dense;               // measuring aid: do the per-score arithmetic even where it is known to give exact zeros
   const int2 *order;       // packed batches: work items by descending weight, see decode_item
   const int2 *order2;      // the same for every second tile (backward only)
   int order_span;          // entries of one sequence that stay neighbours in order / order2 (>= 1)

@@ -30,15 +30,21 @@ namespace sb {
 // kMasked tiles (the diagonal one, or one with rows past the sequence end) zero what is not allowed.
 // The chunk is kept to 16 columns so that the unrolled code of all variants stays inside the instruction cache.
 // mc0: key index of the first column inside the 128-key tile (for the diagonal mask).
+// skip_zero (unmasked chunks only): where the product of (1 - beta) at the END of the chunk -- its largest value in
+// the chunk -- has underflowed to exactly 0 and the prefix of G is still exactly 0, for all 32 rows of the warp, every
+// A, G and dz of the chunk is exactly 0 (e, the reciprocals and dP - dR are finite): only the log-space sum is formed,
+// with the same operations as otherwise, and the rest is not computed.
 template <bool kMasked>
 __device__ __forceinline__ void bwd_row_chunk_values(const uint32_t (&s)[16], const uint32_t (&dp)[16], int mc0, int r, bool diag,
                                                      int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
-                                                     float &gs, float &logsum, float (&pa)[16], float (&pz)[16]) {
+                                                     float &gs, float &logsum, float (&pa)[16], float (&pz)[16],
+                                                     bool skip_zero = false) {
   // columns (tile-local key indices) below `limit` are allowed: one compare per column, no branches
   const int limit = !row_valid ? -1 : (diag ? r + ac : 0x7fffffff);
   const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
   float2 e01[4], e23[4], be01[4], be23[4];
   float rpg[4], q23[4], ri1[4], ri3[4];
+  float2 tt01[4], tt23[4], ppg[4];
 #pragma unroll
   for (int g = 0; g < 4; ++g) {   // independent work in packed pairs (two fp32 per instruction)
     const float2 x01 = mul2(make_float2(__uint_as_float(s[4 * g]), __uint_as_float(s[4 * g + 1])), sc);
@@ -54,9 +60,20 @@ __device__ __forceinline__ void bwd_row_chunk_values(const uint32_t (&s)[16], co
       if (!(col + 3 < limit)) { e23[g].y = 0.f; t23.y = 1.f; }
     }
     const float2 pp = mul2(make_float2(t01.x, t23.x), make_float2(t01.y, t23.y));   // (t0 t1, t2 t3)
-    const float prod = pp.x * pp.y;
-    const float rp = rcp(prod);
-    logsum += lg2(prod);
+    logsum += lg2(pp.x * pp.y);
+    tt01[g] = t01;
+    tt23[g] = t23;
+    ppg[g] = pp;
+  }
+  if (!kMasked && skip_zero && __all_sync(0xffffffffu, ex2(r1 + logsum) == 0.f && gpre + gs == 0.f)) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { pa[i] = 0.f; pz[i] = 0.f; }
+    return;
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const float2 t01 = tt01[g], t23 = tt23[g], pp = ppg[g];
+    const float rp = rcp(pp.x * pp.y);
     const float2 ab = mul2(make_float2(rp, rp), make_float2(pp.y, pp.x));           // (1 / t0 t1, 1 / t2 t3)
     const float2 ri01 = mul2(make_float2(ab.x, ab.x), make_float2(t01.y, t01.x));   // (1/t0, 1/t1)
     const float2 ri23 = mul2(make_float2(ab.y, ab.y), make_float2(t23.y, t23.x));   // (1/t2, 1/t3)
@@ -119,9 +136,10 @@ __device__ __forceinline__ void bwd_row_chunk_values(const uint32_t (&s)[16], co
 template <bool kFp16, bool kStoreA, bool kMasked>
 __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&s)[16], const uint32_t (&dp)[16], int c0, int mc0, int r, bool diag,
                                               int ac, bool row_valid, float scale2, float r1, float gpre, float dr,
-                                              float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z) {
+                                              float &gs, float &logsum, uint8_t *tile_a, uint8_t *tile_z,
+                                              bool skip_zero = false) {
   float pa[16], pz[16];
-  bwd_row_chunk_values<kMasked>(s, dp, mc0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
+  bwd_row_chunk_values<kMasked>(s, dp, mc0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz, skip_zero);
   if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0, pa);
   store_row_chunk16<kFp16>(tile_z, r, c0, pz);
 }
@@ -139,7 +157,7 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
                                               uint8_t *tile_a, uint8_t *tile_z, float *mid_r1 = nullptr,
                                               float *mid_s2 = nullptr, uint32_t empty_bar = 0, uint32_t gate_bar = 0,
                                               uint32_t gate_parity = 0, unsigned short *az_a = nullptr,
-                                              unsigned short *az_z = nullptr) {
+                                              unsigned short *az_z = nullptr, bool skip_zero = false) {
   uint32_t s0[16], d0[16], s1[16], d1[16];
   bool ok = true;
   tmem_ld16(ts, s0);
@@ -152,7 +170,7 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
     tmem_ld16(tp + c0 + 16, d1);
     {
       float pa[16], pz[16];
-      bwd_row_chunk_values<kMasked>(s0, d0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
+      bwd_row_chunk_values<kMasked>(s0, d0, mc0 + c0, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz, skip_zero);
       if (pair == 0 && gate_bar != 0) {
         ok = mbar_wait(gate_bar, gate_parity);
         tc_fence_after();
@@ -179,7 +197,7 @@ __device__ __forceinline__ bool strip_row_pass(uint32_t ts, uint32_t tp, int r, 
     }
     {
       float pa[16], pz[16];
-      bwd_row_chunk_values<kMasked>(s1, d1, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz);
+      bwd_row_chunk_values<kMasked>(s1, d1, mc0 + c0 + 16, r, diag, ac, row_valid, scale2, r1, gpre, dr, gs, logsum, pa, pz, skip_zero);
       if constexpr (kStoreA) store_row_chunk16<kFp16>(tile_a, r, c0 + 16, pa);
       uint32_t wz[8];
       pack_row_chunk16<kFp16>(pz, wz);
@@ -399,7 +417,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                                        bar(bSpEmpty + w), gate, gate_parity, az_a, az_z);
         else
           pass_ok = strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
-                                                        nullptr, nullptr, bar(bSpEmpty + w), gate, gate_parity, az_a, az_z);
+                                                        nullptr, nullptr, bar(bSpEmpty + w), gate, gate_parity, az_a, az_z, !p.dense);
       } else {
         float *rec_r1 = p.bnd_r1 + rec0 + (long long)u * (2 * kBM);   // quarter 2 (u & 1) of key tile u >> 1
         float *rec_s2 = p.bnd_s2 + rec0 + (long long)u * (2 * kBM);
@@ -411,7 +429,8 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                                        gate, gate_parity);
         else
           pass_ok = strip_row_pass<kFp16, false, false>(tS, tP, r, 0, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, nullptr, gZ,
-                                                        rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w), gate, gate_parity);
+                                                        rec_r1 + kBM, rec_s2 + kBM, bar(bSpEmpty + w), gate, gate_parity, nullptr,
+                                                        nullptr, !p.dense);
       }
       if (!pass_ok) {   // the bounded wait inside the pass gave up
         *abort_flag = 1;
@@ -693,7 +712,7 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (masked)
             bwd_row_chunk_values<true>(s0, d0, quarter * 32, r, diag, p.attend_current, valid, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
           else
-            bwd_row_chunk_values<false>(s0, d0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, pa, pz);
+            bwd_row_chunk_values<false>(s0, d0, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, pa, pz, !p.dense);
           // the A/dz tiles are still being read by the previous step's MMAs
           if (g >= 1) {
             ok = wait_or_abort(bar(bAzEmpty), (g - 1) & 1, abort_flag, p, 631);
@@ -710,7 +729,8 @@ tc_bwd_dkv4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           bwd_row_chunk<kFp16, true, true>(s1, d1, w * 32 + 16, quarter * 32 + 16, r, diag, p.attend_current, valid, scale2, r1f,
                                            gpre, dr, gs, logsum, gA, gZ);
         else
-          bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ);
+          bwd_row_chunk<kFp16, true, false>(s1, d1, w * 32 + 16, 0, r, false, 0, true, scale2, r1f, gpre, dr, gs, logsum, gA, gZ,
+                                            !p.dense);
       } else {
         if (g >= 1) {
           ok = wait_or_abort(bar(bAzEmpty), (g - 1) & 1, abort_flag, p, 631);

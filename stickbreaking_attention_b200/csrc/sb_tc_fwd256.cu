@@ -279,7 +279,7 @@ tc_fwd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // (the P rows of such a warp keep whatever their buffer held: they only reach accumulator rows that are never stored)
         if (!warp_live) {
         } else if (s >= s_diag0) fwd256_row_pass<kFp16, true>(ts, s * kBN, row, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
-        else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r, ts + kPCol);
+        else fwd256_row_pass<kFp16, false>(ts, 0, 0, ac, scale2, R, logsum, tile_p, r, ts + kPCol, !p.dense);
         run += (double)logsum;
         if constexpr (kPTmem) tmem_wait_st();
         tc_fence_before();          // this step's TMEM reads (and writes of P) are done before the slot is handed back

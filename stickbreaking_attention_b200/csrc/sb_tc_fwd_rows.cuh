@@ -90,12 +90,54 @@ __device__ __forceinline__ void fwd256_zero_pair(int c0, uint8_t *tile_p, int r,
   }
 }
 
+// One row of a 64-key sub-tile whose P is known to be exactly zero: only the log-space sum is formed, with the same
+// operations in the same order as fwd256_row_chunk, so that it is the same number bit for bit.
+__device__ __forceinline__ void fwd256_logsum_chunk(const uint32_t (&v)[16], float scale2, float &logsum) {
+  const float2 sc = make_float2(scale2, scale2), one = make_float2(1.f, 1.f);
+#pragma unroll
+  for (int g = 3; g >= 0; --g) {
+    const float2 x01 = mul2(make_float2(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1])), sc);
+    const float2 x23 = mul2(make_float2(__uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3])), sc);
+    const float2 e01 = make_float2(ex2(fminf(x01.x, 30.f)), ex2(fminf(x01.y, 30.f)));
+    const float2 e23 = make_float2(ex2(fminf(x23.x, 30.f)), ex2(fminf(x23.y, 30.f)));
+    const float2 t01 = add2(e01, one), t23 = add2(e23, one);
+    const float p01 = t01.x * t01.y, p23 = t23.x * t23.y;
+    logsum += lg2(p01 * p23);
+  }
+}
+template <bool kFp16>
+__device__ __forceinline__ void fwd256_logsum_pass(uint32_t ts, float scale2, float &logsum, uint8_t *tile_p, int r,
+                                                   uint32_t tmem_p) {
+  uint32_t va[16], vb[16];
+  tmem_ld16(ts + 48, va);
+#pragma unroll 1
+  for (int pair = 1; pair >= 0; --pair) {
+    tmem_wait_ld_regs(va);
+    tmem_ld16(ts + pair * 32, vb);
+    fwd256_logsum_chunk(va, scale2, logsum);
+    tmem_wait_ld_regs(vb);
+    if (pair == 1) tmem_ld16(ts + 16, va);
+    fwd256_logsum_chunk(vb, scale2, logsum);
+  }
+  // P is written last: its columns alias scores that have all been read by now
+  fwd256_zero_pair<kFp16>(32, tile_p, r, tmem_p);
+  fwd256_zero_pair<kFp16>(0, tile_p, r, tmem_p);
+}
+
 // One row of a 64-key sub-tile.  In a masked sub-tile the columns from (last row of this warp) + ac on are masked for
 // every row of the warp (its 32 rows are consecutive and 32-aligned): such 32-column halves are not computed at all,
 // their P is zero and R and logsum stay as they are -- 6 of the 16 (warp, half) pairs of a diagonal 128 x 128 tile.
+// skip_zero: an unmasked sub-tile whose P is exactly zero for the whole warp (R has underflowed) only sums its logs.
 template <bool kFp16, bool kMasked>
 __device__ __forceinline__ void fwd256_row_pass(uint32_t ts, int key0, int row, int ac, float scale2, float &R,
-                                                float &logsum, uint8_t *tile_p, int r, uint32_t tmem_p) {
+                                                float &logsum, uint8_t *tile_p, int r, uint32_t tmem_p,
+                                                bool skip_zero = false) {
+  if (!kMasked && skip_zero && __all_sync(0xffffffffu, R == 0.f)) {
+    // The product over the keys after this sub-tile has underflowed to exactly 0 for all 32 rows of the warp: every
+    // p of the sub-tile is e * 0 = 0 (e is finite: its exponent is clamped) and R stays 0.
+    fwd256_logsum_pass<kFp16>(ts, scale2, logsum, tile_p, r, tmem_p);
+    return;
+  }
   int hi = 1;   // last 32-column half with an allowed key
   if (kMasked) {
     const int span = (row | 31) + ac - key0;   // the warp's rows may attend to columns [0, span) of this sub-tile

@@ -31,6 +31,7 @@ class _Switches(threading.local):
     """Per-thread switches (a trainer may drive several devices from several threads)."""
     force_simt = False
     bwd_recompute = False
+    dense_row_pass = False
 
 
 _state = _Switches()
@@ -62,11 +63,25 @@ def small_backward_workspace(enabled: bool = True):
         _state.bwd_recompute = old
 
 
+@contextlib.contextmanager
+def dense_row_pass(enabled: bool = True):
+    """Within the block (calling thread only) the tensor-core kernels do the per-score arithmetic for every score, also
+    where the product of (1 - beta) over the keys in between has underflowed to exactly 0 for a whole warp and the
+    results are known to be exact zeros (``SB_FLAG_DENSE_ROW_PASS``).  Same results bit for bit; a measuring aid."""
+    old = _state.dense_row_pass
+    _state.dense_row_pass = enabled
+    try:
+        yield
+    finally:
+        _state.dense_row_pass = old
+
+
 def switch_flags() -> int:
     """The calling thread's switches as C-ABI flag bits.  The autograd functions read them in their forward and hand
     them to their backward: autograd runs the backward on a thread of its own, which does not see the caller's."""
     return (_cabi.SB_FLAG_FORCE_SIMT if _state.force_simt else 0) | \
-           (_cabi.SB_FLAG_BWD_RECOMPUTE if _state.bwd_recompute else 0)
+           (_cabi.SB_FLAG_BWD_RECOMPUTE if _state.bwd_recompute else 0) | \
+           (_cabi.SB_FLAG_DENSE_ROW_PASS if _state.dense_row_pass else 0)
 
 
 def kernel_launches() -> int:
