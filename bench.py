@@ -49,8 +49,8 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of this workload.  The figures belong
 # to the kernel sources whose digest is recorded with them: after any change to the kernels they are stale, and
 # `roofline.traffic` is reported as null until a new capture is entered here.
-NCU_TRAFFIC = {"kernel_sources_sha256_16": "f60b7c195a0081ed",
-               "bytes": {"c2": {"fwd": 478.8e6, "bwd_dq": 1452.6e6, "bwd_dkv": 1412.5e6}, "c5s": {"fwd": 2388.0e6}}}
+NCU_TRAFFIC = {"kernel_sources_sha256_16": "e69cbeb77ee1b516",
+               "bytes": {"c2": {"fwd": 495.9e6, "bwd_dq": 1467.1e6, "bwd_dkv": 1407.0e6}, "c5s": {"fwd": 2386.8e6}}}
 
 
 def kernel_sources_digest():
@@ -480,6 +480,14 @@ def run_gpu_arm(args, w):
     ms_reps, launches, clocks = timed(step_resident, args.steps, max(args.warmup, 3), repeats)
     ms_step = statistics.median(ms_reps)
     sb.check_status(device)
+    # The same step with the per-score arithmetic forced for every score (SB_FLAG_DENSE_ROW_PASS): by default the row
+    # passes form only the running log-sum where the weights are exact zeros for a whole warp -- with N(0, 1) inputs that
+    # is most of every sequence -- and this figure says what that is worth (every MMA runs either way).
+    def step_dense():
+        with sb.dense_row_pass():
+            return step_resident()
+    dense_reps, _, _ = timed(step_dense, args.steps, 3, min(repeats, 3))
+    ms_dense = statistics.median(dense_reps)
     host_us = host_time_us(step_resident)
     e2e_steps = max(3, min(args.steps, 20))
     e2e_reps, _, _ = timed(step_e2e, e2e_steps, 3, min(repeats, 3))
@@ -542,6 +550,10 @@ def run_gpu_arm(args, w):
                     "ms_per_step": ms_e2e, "steps": e2e_steps, "repeats": len(e2e_reps),
                     "pinned_gb_per_s_per_rank": (h2d + d2h) / (ms_e2e * 1e-3) / 1e9,
                     "overlap": "h2d of step i+1 and d2h of step i-1 run on their own streams while step i computes"},
+            "dense_row_pass": {"value": fl * world / (ms_dense * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_dense,
+                               "repeats": len(dense_reps),
+                               "note": "same step with SB_FLAG_DENSE_ROW_PASS: the row passes evaluate every score, also "
+                                       "where a whole warp's weights are exact zeros (bit-identical results)"},
             "gpu_launches": launches * repeats,
             "gpu_launches_per_repetition": launches,
             "clocks": clocks,
