@@ -236,7 +236,7 @@ constexpr int kKvTile = 2 * kKvBox;            // K or V sub-tile
 constexpr int kStageBytes = 2 * kKvTile;
 constexpr int kZBytes = kBM * kBN * 2;         // dz tile: 128 rows x 64 keys
 constexpr int kSmem = 1024 + 4 * kTileBytes + kStages * kStageBytes + 2 * kZBytes + 512;
-enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bDqFull = 14, bSpEmpty = 12, bNum = 16 };
+enum { bQG = 0, bKvFull = 1, bKvEmpty = 3, bSpFull = 5, bZFull = 7, bZEmpty = 9, bFirst = 11, bSpEmpty = 12, bDqFull = 14, bNum = 16 };
 }  // namespace dq2
 
 template <bool kFp16>
@@ -277,6 +277,7 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(bar(bQG), 1);
+    mbar_init(bar(bFirst), 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(bar(bKvFull + s), 1); mbar_init(bar(bKvEmpty + s), issuers); }
     for (int w = 0; w < 2; ++w) {
       mbar_init(bar(bSpFull + w), 1);
@@ -338,8 +339,13 @@ tc_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       };
       bool ok = wait_or_abort(bar(bQG), 0, abort_flag, p, 520) && wait_or_abort(bar(bKvFull), 0, abort_flag, p, 521);
       // tile b starts once tile a's first scores are done, so that one tile's MMAs fall into the other's row pass
-      if (ok && w == 1 && steps_a > 0) ok = wait_or_abort(bar(bSpFull + 0), 0, abort_flag, p, 525);
-      if (ok) { tc_fence_after(); issue_sp(0); }
+      // (bFirst completes exactly once: this waiter does not follow the phases of tile a's own barriers)
+      if (ok && w == 1 && steps_a > 0) ok = wait_or_abort(bar(bFirst), 0, abort_flag, p, 525);
+      if (ok) {
+        tc_fence_after();
+        issue_sp(0);
+        if (w == 0) mma_commit(bar(bFirst));
+      }
       for (int u = 0; ok && u < my_steps; ++u) {
         // the rows of step u have read their S/dP (they are still computing): the next scores go first ...
         if (u + 1 < my_steps) {
