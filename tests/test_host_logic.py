@@ -141,3 +141,22 @@ def test_functional_operator_traces_without_a_device():
     o, rem, log_rem = (n.meta["val"] for n in gm.graph.find_nodes(op="output")[0].args[0])
     assert o.shape == q.shape and o.stride() == q.stride() and o.dtype == q.dtype
     assert rem.shape == q.shape[:-1] and log_rem.shape == q.shape[:-1] and log_rem.dtype == torch.float64
+
+
+def test_switches_are_per_thread_and_travel_as_flags():
+    """The context managers set C-ABI flag bits for the calling thread only; autograd hands them to its own thread
+    through the saved context, so another thread must not see them."""
+    import threading
+    from stickbreaking_attention_b200 import _cabi, ops
+    import stickbreaking_attention_b200 as sb
+    assert ops.switch_flags() == 0
+    seen = {}
+    with sb.dense_row_pass(), sb.small_backward_workspace():
+        assert ops.switch_flags() == _cabi.SB_FLAG_DENSE_ROW_PASS | _cabi.SB_FLAG_BWD_RECOMPUTE
+        t = threading.Thread(target=lambda: seen.setdefault("other", ops.switch_flags()))
+        t.start()
+        t.join()
+        with sb.force_simt():
+            assert ops.switch_flags() & _cabi.SB_FLAG_FORCE_SIMT
+        assert not ops.switch_flags() & _cabi.SB_FLAG_FORCE_SIMT
+    assert seen["other"] == 0 and ops.switch_flags() == 0
