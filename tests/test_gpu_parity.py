@@ -444,14 +444,14 @@ def test_both_forward_kernels_for_small_heads(sb, cuda_device, dtype, d, ac):
 
 
 @pytest.mark.parametrize("mode", ["stored", "recompute"])
-@pytest.mark.parametrize("d", [128, 64])
-def test_skipping_exact_zeros_changes_no_bit(sb, cuda_device, d, mode):
+@pytest.mark.parametrize("d,dtype", [(128, torch.bfloat16), (64, torch.bfloat16), (96, torch.float16)])
+def test_skipping_exact_zeros_changes_no_bit(sb, cuda_device, d, dtype, mode):
     """With N(0, 1) inputs the product of (1 - beta) underflows to exactly 0 about a hundred keys before the query; the
     kernels then skip the arithmetic whose results are exact zeros.  Forced to do it all the same
     (SB_FLAG_DENSE_ROW_PASS), they must return the same bits: o, rem and all three gradients."""
     import contextlib
     lengths = [1500, 700, 300, 2100]
-    ins = H.make_inputs((3, sum(lengths), d), torch.bfloat16, seed=23 + d, std=1.0)
+    ins = H.make_inputs((3, sum(lengths), d), dtype, seed=23 + d, std=1.0)
     cu = cu_of(lengths)
     small = sb.small_backward_workspace() if mode == "recompute" else contextlib.nullcontext()
     with small:
@@ -460,7 +460,7 @@ def test_skipping_exact_zeros_changes_no_bit(sb, cuda_device, d, mode):
             dense = H.run_varlen(sb, *ins, cu, cuda_device, max_seqlens=max(lengths))
     for name, a, b in zip(("o", "rem", "dq", "dk", "dv"), fast, dense):
         assert torch.equal(a, b), name
-    H.assert_parity(fast, H.oracle_varlen(*ins, cu), torch.bfloat16, "zeros skipped")
+    H.assert_parity(fast, H.oracle_varlen(*ins, cu), dtype, "zeros skipped")
 
 
 # ---- error behaviour: failures are made on the host, never by faulting the device -----------------------
